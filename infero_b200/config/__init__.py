@@ -1,7 +1,8 @@
 from .spec import (BlockSpec, FeedForwardSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec,
                    ScheduleEntry)
 from .qwen2 import ConfigError, Qwen2Config
+from .vufizen import VufizenConfig
 from .engine_config import EngineConfig
 
 __all__ = ["BlockSpec", "FeedForwardSpec", "MixerSpec", "ModelSpec", "NormSpec", "PositionSpec",
-           "ScheduleEntry", "ConfigError", "Qwen2Config", "EngineConfig"]
+           "ScheduleEntry", "ConfigError", "Qwen2Config", "VufizenConfig", "EngineConfig"]

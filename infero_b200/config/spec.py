@@ -34,6 +34,17 @@ def _name_map(given, defaults) -> dict:
 ATTENTION_NAMES = (("q", "self_attn.q_proj"), ("k", "self_attn.k_proj"), ("v", "self_attn.v_proj"),
                    ("o", "self_attn.o_proj"))
 SWIGLU_NAMES = (("gate", "mlp.gate_proj"), ("up", "mlp.up_proj"), ("down", "mlp.down_proj"))
+# Mixers and feed-forwards with more tensors than those: the roles they know, with default leaf names.
+DIFF_ATTENTION_NAMES = (("q", "mix.q"), ("k", "mix.k"), ("v", "mix.v"), ("o", "mix.o"),
+                        ("q_conv", "mix.q.conv"), ("k_conv", "mix.k.conv"), ("v_conv", "mix.v.conv"),
+                        ("q_norm", "mix.q.norm"), ("k_norm", "mix.k.norm"),
+                        ("lq1", "mix.lq1"), ("lk1", "mix.lk1"), ("lq2", "mix.lq2"), ("lk2", "mix.lk2"))
+HGRN2_NAMES = (("q", "mix.q"), ("f", "mix.f"), ("f_bias", "mix.f.b"), ("lower", "mix.lower"), ("v", "mix.v"),
+               ("out_norm", "mix.norm"), ("o", "mix.o"))
+MOE_NAMES = (("expert", "mlp.e{}"), ("gate", "gate"), ("up", "up"), ("down", "down"), ("router", "mlp.router"),
+             ("shared", "mlp.shared"), ("shared_gate", "mlp.shared.sg"))
+MIXER_NAMES = {"diff_attention": DIFF_ATTENTION_NAMES, "hgrn2": HGRN2_NAMES}
+FEED_FORWARD_NAMES = {"moe_swiglu": MOE_NAMES}
 
 
 @dataclass(frozen=True)
@@ -42,6 +53,7 @@ class PositionSpec:
 
     kind "rope_neox": pairs (i, i + rotary_dim/2), angle = pos * theta^(-2i/rotary_dim)
     (crates/kernels/src/cu/ops.cu:488-523, crates/kernels/src/cpu/mod.rs:275-314).
+    kind "rope_interleaved": the same angles on adjacent pairs (2i, 2i + 1).
     """
     kind: str
     theta: float
@@ -50,7 +62,8 @@ class PositionSpec:
 
 @dataclass(frozen=True)
 class NormSpec:
-    """kind "rmsnorm": x * rsqrt(mean(x^2) + eps) * w (crates/kernels/src/cu/ops.cu:44-62)."""
+    """kind "rmsnorm": x * rsqrt(mean(x^2) + eps) * w (crates/kernels/src/cu/ops.cu:44-62).
+    kind "rmsnorm_scalar": the same with w a single stored number for all coordinates."""
     kind: str
     dim: int
     eps: float
@@ -63,6 +76,17 @@ class MixerSpec:
     kind "gqa_attention": grouped-query attention over the paged cache.  ``window`` is
     None for all keys, or W so that key j is visible from query p iff j <= p and
     p - j < W.
+
+    kind "diff_attention": every head has two attention maps of width ``head_dim`` over the same values
+    of width ``value_dim``; their results a1, a2 combine to a1 - lambda a2 with one lambda per layer,
+    exp(lq1 . lk1) - exp(lq2 . lk2) + ``diff``, followed by a weightless RMS norm over the value width and
+    the factor 1 - ``diff``.  ``conv_taps`` > 0 puts a causal convolution over time on every channel of
+    q, k and v right behind the projection; ``qk_norm`` an RMS norm (shared weight over ``head_dim``) on
+    every map of every query and key head before the rotation.
+
+    kind "hgrn2": a gated linear recurrence with a ``head_dim`` x ``value_dim`` state per head whose
+    forget gate (bounded below by a stored vector) also scales what is written; the result of a head is
+    RMS-normed over ``value_dim`` with a shared weight.  ``norm_eps`` is the eps of the norms inside a mixer.
     """
     kind: str
     hidden: int
@@ -74,10 +98,16 @@ class MixerSpec:
     scale: float = 0.0
     window: Optional[int] = None
     position: Optional[PositionSpec] = None
+    value_dim: int = 0                # width of a head's value; 0: head_dim
+    conv_taps: int = 0
+    qk_norm: bool = False
+    norm_eps: float = 1e-6
+    diff: float = 0.0
     # free-form extras for mixers defined outside the framework
     extra: Tuple[Tuple[str, object], ...] = ()
     # role -> leaf name under the block's prefix (see ATTENTION_NAMES); roles not given keep the default
     names: Tuple[Tuple[str, str], ...] = ()
+    weight_suffix: str = ".weight"    # what follows a matrix's leaf name in the checkpoint
 
     def get(self, key, default=None):
         for k, v in self.extra:
@@ -86,20 +116,33 @@ class MixerSpec:
         return default
 
     def tensor_names(self) -> dict:
-        return _name_map(self.names, ATTENTION_NAMES)
+        return _name_map(self.names, MIXER_NAMES.get(self.kind, ATTENTION_NAMES))
+
+    @property
+    def v_dim(self) -> int:
+        return self.value_dim or self.head_dim
 
 
 @dataclass(frozen=True)
 class FeedForwardSpec:
-    """kind "swiglu": down(silu(gate(x)) * up(x)) (crates/model/src/lib.rs:7391-7451)."""
+    """kind "swiglu": down(silu(gate(x)) * up(x)) (crates/model/src/lib.rs:7391-7451).
+
+    kind "moe_swiglu": ``experts`` SwiGLU experts of width ``intermediate`` of which every token uses the
+    ``top`` with the largest router logits, weighted by the softmax over those logits alone; with
+    ``shared_intermediate`` > 0 a SwiGLU expert of that width runs for every token and is added, times
+    sigmoid(w . x) of a stored vector w."""
     kind: str
     hidden: int
     intermediate: int
+    experts: int = 0
+    top: int = 0
+    shared_intermediate: int = 0
     extra: Tuple[Tuple[str, object], ...] = ()
     names: Tuple[Tuple[str, str], ...] = ()          # role -> leaf name (see SWIGLU_NAMES)
+    weight_suffix: str = ".weight"
 
     def tensor_names(self) -> dict:
-        return _name_map(self.names, SWIGLU_NAMES)
+        return _name_map(self.names, FEED_FORWARD_NAMES.get(self.kind, SWIGLU_NAMES))
 
 
 @dataclass(frozen=True)
@@ -107,16 +150,23 @@ class BlockSpec:
     """One layer: its parts and the tensor-name prefix its weights live under.
 
     kind "prenorm": x += mixer(norm1(x)); x += ffn(norm2(x)).
+    kind "gated_postnorm": the sublayers read x itself and the norm sits on their result:
+    x += norm1(mixer(x) * sigmoid(G1 x + b1)); x += norm2(ffn(x) * sigmoid(G2 x + b2)); the gates are
+    there where ``mixer_gate_name`` / ``ffn_gate_name`` are given (bias: that name + ``gate_bias_suffix``),
+    and ``ffn`` may be None (a layer with a mixer only).
     """
     kind: str
     prefix: str
     mixer: MixerSpec
-    ffn: FeedForwardSpec
+    ffn: Optional[FeedForwardSpec]
     mixer_norm: NormSpec
-    ffn_norm: NormSpec
+    ffn_norm: Optional[NormSpec]
     # leaf names of the two norm weights under the prefix
     mixer_norm_name: str = "input_layernorm.weight"
     ffn_norm_name: str = "post_attention_layernorm.weight"
+    mixer_gate_name: Optional[str] = None
+    ffn_gate_name: Optional[str] = None
+    gate_bias_suffix: str = ".b"
 
 
 @dataclass(frozen=True)

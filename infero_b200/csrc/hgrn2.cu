@@ -1,0 +1,138 @@
+// HGRN2: gated linear recurrence with a matrix state per head, in which the forget gate also
+// decides what is written.  Per head, with q_t (D), f_t in (0,1)^D and v_t (V):
+//
+//   S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T        S is D x V, 32-bit, one per request and head
+//   o_t = S_t^T q_t                                  then o_t / sqrt(mean(o_t^2) + eps) * w  over V
+//
+// q_t = silu(q'_t), f_t = l + (1 - l) sigmoid(f'_t + b) with q', f', v rows of one stacked product.
+// One block per (head, request of the step) walks that request's new tokens in order, from the state
+// the steps before left in the request's slot, and leaves the state behind; a step of one token is
+// the same walk of length one.  Thread (j, s) keeps rows s*DPT .. s*DPT+DPT-1 of column j of S in
+// registers; tokens are staged eight at a time in shared memory with the activations applied once.
+#include "common.cuh"
+
+namespace {
+
+constexpr int TT = 8;      // tokens staged per round
+
+template <typename T, int DPT>
+__global__ void __launch_bounds__(512)
+hgrn2_scan_kernel(const float* __restrict__ proj, int stride, int q_off, int f_off, int v_off,
+                  const float* __restrict__ f_bias, const float* __restrict__ lower,
+                  const float* __restrict__ out_w, float eps, float* __restrict__ state,
+                  const int* __restrict__ entry_q_start, const int* __restrict__ entry_q_len,
+                  const int* __restrict__ entry_slot, T* __restrict__ out, int out_stride,
+                  int H, int D, int V, int DS) {
+    extern __shared__ float sm[];
+    float* qs = sm;                      // [TT][D]
+    float* fs = qs + TT * D;             // [TT][D]
+    float* vs = fs + TT * D;             // [TT][V]
+    float* part = vs + TT * V;           // [TT][DS][V]
+    const int h = blockIdx.x, e = blockIdx.y;
+    const int row0 = entry_q_start[e], n = entry_q_len[e], slot = entry_slot[e];
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    const int j = tid % V, s = tid / V;
+    const bool active = s < DS;
+    const int i0 = s * DPT;
+    float S[DPT];
+    float* st = state + (((size_t)slot * H + h) * D) * V;
+#pragma unroll
+    for (int ii = 0; ii < DPT; ++ii) S[ii] = (active && i0 + ii < D) ? st[(size_t)(i0 + ii) * V + j] : 0.f;
+    const int lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
+    for (int t0 = 0; t0 < n; t0 += TT) {
+        const int nt = min(TT, n - t0);
+        __syncthreads();
+        for (int idx = tid; idx < nt * D; idx += nthreads) {
+            const int tt = idx / D, i = idx - tt * D;
+            const float* pr = proj + (size_t)(row0 + t0 + tt) * stride;
+            const float qv = pr[q_off + h * D + i];
+            qs[tt * D + i] = qv / (1.0f + expf(-qv));
+            const float fr = pr[f_off + h * D + i] + f_bias[h * D + i];
+            const float l = lower[h * D + i];
+            fs[tt * D + i] = l + (1.0f - l) * (1.0f / (1.0f + expf(-fr)));
+        }
+        for (int idx = tid; idx < nt * V; idx += nthreads) {
+            const int tt = idx / V, jj = idx - tt * V;
+            vs[tt * V + jj] = proj[(size_t)(row0 + t0 + tt) * stride + v_off + h * V + jj];
+        }
+        __syncthreads();
+        if (active) {
+            for (int tt = 0; tt < nt; ++tt) {
+                const float vj = vs[tt * V + j];
+                float o = 0.f;
+#pragma unroll
+                for (int ii = 0; ii < DPT; ++ii) {
+                    if (i0 + ii < D) {
+                        const float f = fs[tt * D + i0 + ii];
+                        S[ii] = fmaf(f, S[ii], (1.0f - f) * vj);
+                        o = fmaf(S[ii], qs[tt * D + i0 + ii], o);
+                    }
+                }
+                part[(tt * DS + s) * V + j] = o;
+            }
+        }
+        __syncthreads();
+        for (int tt = warp; tt < nt; tt += nwarps) {
+            float ss = 0.f;
+            for (int jj = lane; jj < V; jj += 32) {
+                float o = 0.f;
+                for (int k = 0; k < DS; ++k) o += part[(tt * DS + k) * V + jj];
+                part[(tt * DS) * V + jj] = o;
+                ss = fmaf(o, o, ss);
+            }
+            ss = warp_sum(ss);
+            const float r = 1.0f / sqrtf(ss / (float)V + eps);
+            T* orow = out + (size_t)(row0 + t0 + tt) * out_stride + (size_t)h * V;
+            for (int jj = lane; jj < V; jj += 32) orow[jj] = from_f32<T>(part[(tt * DS) * V + jj] * r * out_w[jj]);
+        }
+    }
+    if (active) {
+#pragma unroll
+        for (int ii = 0; ii < DPT; ++ii)
+            if (i0 + ii < D) st[(size_t)(i0 + ii) * V + j] = S[ii];
+    }
+}
+
+template <typename T, int DPT>
+int launch(const float* proj, int stride, int q_off, int f_off, int v_off, const float* f_bias, const float* lower,
+           const float* out_w, float eps, float* state, const int* qs, const int* ql, const int* es, void* out,
+           int out_stride, int E, int H, int D, int V, cudaStream_t stream) {
+    const int DS = (D + DPT - 1) / DPT;
+    const int threads = ((V * DS + 31) / 32) * 32;
+    const size_t smem = (size_t)TT * (2 * D + V + DS * V) * sizeof(float);
+    auto kern = hgrn2_scan_kernel<T, DPT>;
+    if (smem > 48 * 1024) {
+        INFERO_REQUIRE(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess,
+                       "hgrn2: %zu bytes of shared memory are not available", smem);
+    }
+    kern<<<dim3(H, E), threads, smem, stream>>>(proj, stride, q_off, f_off, v_off, f_bias, lower, out_w, eps, state,
+                                                qs, ql, es, (T*)out, out_stride, H, D, V, DS);
+    return infero_check_launch("hgrn2_scan");
+}
+
+}  // namespace
+
+extern "C" {
+
+// proj: float32 [tokens, stride] holding q' at column q_off (H*D), f' at f_off (H*D), v at v_off (H*V).
+// state: float32 [slots, H, D, V].  out: [tokens, H*V] of out_dtype.
+int infero_hgrn2_scan(const float* proj, int stride, int q_off, int f_off, int v_off, const float* f_bias,
+                      const float* lower, const float* out_w, float eps, float* state, const int* entry_q_start,
+                      const int* entry_q_len, const int* entry_slot, void* out, int out_dtype, int out_stride,
+                      int n_entries, int H, int D, int V, cudaStream_t stream) {
+    if (n_entries == 0) return 0;
+    INFERO_REQUIRE(H > 0 && D > 0 && V > 0 && V <= 512, "hgrn2: bad sizes H=%d D=%d V=%d", H, D, V);
+    int dpt = 8;
+    while (dpt < 32 && V * ((D + dpt - 1) / dpt) > 512) dpt *= 2;
+    INFERO_REQUIRE(V * ((D + dpt - 1) / dpt) <= 512, "hgrn2: a state of %d x %d per head is too large", D, V);
+#define GO(TY, N) return launch<TY, N>(proj, stride, q_off, f_off, v_off, f_bias, lower, out_w, eps, state, \
+                                       entry_q_start, entry_q_len, entry_slot, out, out_stride, n_entries, H, D, V, stream)
+    if (out_dtype == INFERO_F32) {
+        if (dpt == 8) GO(float, 8); if (dpt == 16) GO(float, 16); GO(float, 32);
+    } else {
+        if (dpt == 8) GO(bf16, 8); if (dpt == 16) GO(bf16, 16); GO(bf16, 32);
+    }
+#undef GO
+}
+
+}  // extern "C"

@@ -1,0 +1,155 @@
+// Mixture of experts: routing, and the experts of few tokens.
+//
+// route: per token the router's logits z = Wr h in 32-bit, the `top` largest (lowest index wins a tie),
+//   their weights = softmax over the chosen logits only; optionally the gate of a shared expert,
+//   sigmoid(w_sg . h).  One warp per token.
+// experts of few tokens (a weight-streaming path; every (token, choice) reads its expert's rows):
+//   up:   act[t, c, j] = silu(Wg_e[j] . h_t) * (Wu_e[j] . h_t),  e = choice c of token t; one warp per j
+//   down: y[t, i] = sum_c weight[t, c] * (Wd_e[i] . act[t, c]) (+ gate_t * shared[t, i]); one warp per i,
+//         choices added in ascending c, so a token's result does not depend on the batch.
+// Expert weights are stacked: gate_up [E, 2 ff, d] with rows alternating gate_j, up_j; down [E, d, ff].
+#include "common.cuh"
+#include <math_constants.h>
+
+namespace {
+
+constexpr int RWARPS = 4;
+constexpr int MAX_E = 512;
+constexpr int MAX_TOP = 32;
+
+template <typename T>
+__device__ __forceinline__ float warp_dot(const T* __restrict__ a, const T* __restrict__ b, int n, int lane) {
+    float s = 0.f;
+    for (int i = lane; i < n; i += 32) s = fmaf(to_f32(a[i]), to_f32(b[i]), s);
+    return warp_sum(s);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(RWARPS * 32)
+moe_route_kernel(const T* __restrict__ h, int h_stride, const T* __restrict__ router, const T* __restrict__ shared_gate,
+                 int* __restrict__ top_idx, float* __restrict__ top_w, float* __restrict__ gate_out,
+                 int n_tokens, int d, int E, int top) {
+    __shared__ float z[RWARPS][MAX_E];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * RWARPS + warp;
+    if (t >= n_tokens) return;
+    const T* hr = h + (size_t)t * h_stride;
+    for (int e = 0; e < E; ++e) {
+        const float v = warp_dot(router + (size_t)e * d, hr, d, lane);
+        if (lane == 0) z[warp][e] = v;
+    }
+    if (shared_gate) {
+        const float v = warp_dot(shared_gate, hr, d, lane);
+        if (lane == 0) gate_out[t] = 1.0f / (1.0f + expf(-v));
+    }
+    __syncwarp();
+    float first = 0.f, mine = 0.f, sum = 0.f;
+    int mine_e = 0;
+    for (int c = 0; c < top; ++c) {
+        float best = -CUDART_INF_F;
+        int be = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = z[warp][e];
+            if (v > best) best = v, be = e;               // ascending e: the lowest index of equal values stays
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            if (ov > best || (ov == best && oe < be)) best = ov, be = oe;
+        }
+        if (c == 0) first = best;
+        const float p = expf(best - first);
+        sum += p;
+        if (lane == c) mine = p, mine_e = be;
+        __syncwarp();
+        if (lane == 0) z[warp][be] = -CUDART_INF_F;
+        __syncwarp();
+    }
+    if (lane < top) {
+        top_idx[(size_t)t * top + lane] = mine_e;
+        top_w[(size_t)t * top + lane] = mine / sum;
+    }
+}
+
+constexpr int EWARPS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(EWARPS * 32)
+moe_up_kernel(const T* __restrict__ h, int h_stride, const T* __restrict__ gate_up, const int* __restrict__ top_idx,
+              T* __restrict__ act, int d, int ff, int top) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int item = blockIdx.y;                              // token * top + choice
+    const int t = item / top;
+    const int j = blockIdx.x * EWARPS + warp;
+    if (j >= ff) return;
+    const int e = top_idx[item];
+    const T* hr = h + (size_t)t * h_stride;
+    const T* wg = gate_up + ((size_t)e * 2 * ff + 2 * j) * d;
+    const float g = warp_dot(wg, hr, d, lane);
+    const float u = warp_dot(wg + d, hr, d, lane);
+    if (lane == 0) act[(size_t)item * ff + j] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(EWARPS * 32)
+moe_down_kernel(const T* __restrict__ act, const T* __restrict__ down, const int* __restrict__ top_idx,
+                const float* __restrict__ top_w, const float* __restrict__ shared, const float* __restrict__ shared_gate,
+                float* __restrict__ y, int d, int ff, int top) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.y;
+    const int i = blockIdx.x * EWARPS + warp;
+    if (i >= d) return;
+    float acc = 0.f;
+    for (int c = 0; c < top; ++c) {
+        const int e = top_idx[(size_t)t * top + c];
+        const float v = warp_dot(down + ((size_t)e * d + i) * ff, act + ((size_t)t * top + c) * ff, ff, lane);
+        acc = fmaf(top_w[(size_t)t * top + c], v, acc);
+    }
+    if (lane == 0) {
+        if (shared) acc = fmaf(shared_gate ? shared_gate[t] : 1.0f, shared[(size_t)t * d + i], acc);
+        y[(size_t)t * d + i] = acc;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int infero_moe_route(const void* h, int h_stride, const void* router, const void* shared_gate, int dtype, int* top_idx,
+                     float* top_w, float* gate_out, int n_tokens, int d, int E, int top, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    INFERO_REQUIRE(E >= 1 && E <= MAX_E && top >= 1 && top <= E && top <= MAX_TOP,
+                   "moe route: %d experts (at most %d), top %d (at most %d)", E, MAX_E, top, MAX_TOP);
+    const unsigned blocks = (n_tokens + RWARPS - 1) / RWARPS;
+    if (dtype == INFERO_F32)
+        moe_route_kernel<float><<<blocks, RWARPS * 32, 0, stream>>>((const float*)h, h_stride, (const float*)router,
+            (const float*)shared_gate, top_idx, top_w, gate_out, n_tokens, d, E, top);
+    else
+        moe_route_kernel<bf16><<<blocks, RWARPS * 32, 0, stream>>>((const bf16*)h, h_stride, (const bf16*)router,
+            (const bf16*)shared_gate, top_idx, top_w, gate_out, n_tokens, d, E, top);
+    return infero_check_launch("moe_route");
+}
+
+// act: [tokens * top, ff] of dtype (scratch); y float32 [tokens, d]; shared float32 [tokens, d] or null.
+int infero_moe_experts_streamed(const void* h, int h_stride, const void* gate_up, const void* down, int dtype,
+                                const int* top_idx, const float* top_w, const float* shared, const float* shared_gate,
+                                void* act, float* y, int n_tokens, int d, int ff, int top, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    INFERO_REQUIRE(n_tokens * (long long)top <= 65535 && n_tokens <= 65535, "moe: %d tokens are too many for the streaming path", n_tokens);
+    const dim3 gu((ff + EWARPS - 1) / EWARPS, n_tokens * top), gd((d + EWARPS - 1) / EWARPS, n_tokens);
+    if (dtype == INFERO_F32) {
+        moe_up_kernel<float><<<gu, EWARPS * 32, 0, stream>>>((const float*)h, h_stride, (const float*)gate_up, top_idx,
+                                                            (float*)act, d, ff, top);
+        moe_down_kernel<float><<<gd, EWARPS * 32, 0, stream>>>((const float*)act, (const float*)down, top_idx, top_w,
+                                                              shared, shared_gate, y, d, ff, top);
+    } else {
+        moe_up_kernel<bf16><<<gu, EWARPS * 32, 0, stream>>>((const bf16*)h, h_stride, (const bf16*)gate_up, top_idx,
+                                                           (bf16*)act, d, ff, top);
+        moe_down_kernel<bf16><<<gd, EWARPS * 32, 0, stream>>>((const bf16*)act, (const bf16*)down, top_idx, top_w,
+                                                             shared, shared_gate, y, d, ff, top);
+    }
+    return infero_check_launch("moe_experts_streamed");
+}
+
+}  // extern "C"

@@ -1,0 +1,134 @@
+"""Wrappers of the kernels behind the gated post-norm block, the HGRN2 and differential-attention mixers
+and the mixture-of-experts feed-forward (``csrc/gated_norm.cu``, ``hgrn2.cu``, ``diff_attention.cu``,
+``moe.cu``).  Small vectors (biases, norm weights, convolution taps) are float32 on both precisions."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_longlong
+from typing import Optional
+
+import torch
+
+from . import _check, _dt, _i32, _ptr, _stream, lib
+
+
+def _f32(t: Optional[torch.Tensor], name: str) -> Optional[torch.Tensor]:
+    if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+        raise TypeError(f"{name} must be a contiguous float32 tensor")
+    return t
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out (bf16) = x (float32), elementwise."""
+    assert x.dtype == torch.float32 and out.dtype == torch.bfloat16 and x.is_contiguous() and out.is_contiguous()
+    assert x.numel() == out.numel()
+    _check(lib().infero_cast_rows_bf16(_ptr(x), _ptr(out), c_longlong(x.numel()), _stream()))
+
+
+def gated_scalar_norm_add(x: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor],
+                          gate_bias: Optional[torch.Tensor], norm_w: torch.Tensor, eps: float,
+                          h_out: Optional[torch.Tensor] = None) -> None:
+    """z = y * sigmoid(gate + gate_bias) (z = y without a gate); x += z / sqrt(mean(z^2) + eps) * norm_w[0];
+    ``h_out`` (bf16) receives the new x.  x, y, gate float32 (y and gate may be column slices)."""
+    T, d = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and y.shape == (T, d) and y.stride(1) == 1
+    _f32(norm_w, "norm_w"), _f32(gate_bias, "gate_bias")
+    assert y.dtype == torch.float32 and (gate is None or (gate.dtype == torch.float32 and gate.shape == (T, d) and gate.stride(1) == 1))
+    assert h_out is None or (h_out.dtype == torch.bfloat16 and h_out.is_contiguous() and h_out.shape == (T, d))
+    _check(lib().infero_gated_scalar_norm_add(_ptr(x), _ptr(y), c_int(y.stride(0)), _ptr(gate),
+                                              c_int(gate.stride(0) if gate is not None else 0), _ptr(gate_bias),
+                                              _ptr(norm_w), c_float(eps), _ptr(h_out), c_int(T), c_int(d), _stream()))
+
+
+def hgrn2_scan(proj: torch.Tensor, q_off: int, f_off: int, v_off: int, f_bias: torch.Tensor, lower: torch.Tensor,
+               out_w: torch.Tensor, eps: float, state: torch.Tensor, entry_q_start: torch.Tensor,
+               entry_q_len: torch.Tensor, entry_slot: torch.Tensor, out: torch.Tensor, n_entries: int,
+               H: int, D: int, V: int) -> None:
+    """The recurrence of every request of the step over its new tokens; see csrc/hgrn2.cu.
+    proj float32 [T, >= ...] (row stride free); state float32 [slots, H, D, V]; out [T, H*V]."""
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
+    assert tuple(state.shape[1:]) == (H, D, V) and out.shape[1] == H * V and out.stride(1) == 1
+    _f32(f_bias, "f_bias"), _f32(lower, "lower"), _f32(out_w, "out_w")
+    _check(lib().infero_hgrn2_scan(_ptr(proj), c_int(proj.stride(0)), c_int(q_off), c_int(f_off), c_int(v_off),
+                                   _ptr(f_bias), _ptr(lower), _ptr(out_w), c_float(eps), _ptr(state),
+                                   _ptr(_i32(entry_q_start, "entry_q_start")), _ptr(_i32(entry_q_len, "entry_q_len")),
+                                   _ptr(_i32(entry_slot, "entry_slot")), _ptr(out), c_int(_dt(out)), c_int(out.stride(0)),
+                                   c_int(n_entries), c_int(H), c_int(D), c_int(V), _stream()))
+
+
+def qkv_prepare(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int, conv_state: Optional[torch.Tensor],
+                q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
+                inv_freq: Optional[torch.Tensor], positions, tok_entry, entry_q_start, entry_slot, block_table,
+                q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int, n_q_units: int,
+                n_k_units: int, G: int, D: int, V: int, write_cache: bool = True) -> None:
+    """Convolution over time, per-map RMS norm, adjacent-pair rotary, q to ``q_out``, k and v to their pages;
+    see csrc/diff_attention.cu."""
+    T = q_out.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and q_out.stride(1) == 1
+    assert k_cache.dtype == q_out.dtype == v_cache.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert k_cache.shape[-1] == (n_k_units // G) * D and v_cache.shape[-1] == V and k_cache.shape[1] == G
+    _f32(conv_w, "conv_w"), _f32(conv_state, "conv_state"), _f32(q_norm, "q_norm"), _f32(k_norm, "k_norm")
+    rot = 0 if inv_freq is None else 2 * inv_freq.numel()
+    _check(lib().infero_qkv_prepare(
+        _ptr(proj), c_int(proj.stride(0)), _ptr(conv_w), c_int(taps), _ptr(conv_state), _ptr(q_norm), _ptr(k_norm),
+        c_float(eps), _ptr(_f32(inv_freq, "inv_freq")), c_int(rot), _ptr(_i32(positions, "positions")),
+        _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(entry_q_start, "entry_q_start")),
+        _ptr(_i32(entry_slot, "entry_slot")), _ptr(_i32(block_table, "block_table")), c_int(block_table.shape[1]),
+        _ptr(q_out), c_int(q_out.stride(0)), _ptr(k_cache), _ptr(v_cache), c_int(_dt(q_out)), c_int(page_size),
+        c_int(T), c_int(n_q_units), c_int(n_k_units), c_int(G), c_int(D), c_int(V), c_int(1 if write_cache else 0),
+        _stream()))
+
+
+def conv_state_update(proj: torch.Tensor, conv_state: torch.Tensor, taps: int, entry_q_start, entry_q_len,
+                      entry_slot, n_entries: int, channels: int) -> None:
+    """The last taps - 1 product rows of every request become its state (float32 [slots, taps-1, channels])."""
+    assert conv_state.dtype == torch.float32 and conv_state.is_contiguous()
+    assert tuple(conv_state.shape[1:]) == (taps - 1, channels)
+    _check(lib().infero_conv_state_update(_ptr(proj), c_int(proj.stride(0)), _ptr(conv_state), c_int(taps),
+                                          _ptr(_i32(entry_q_start, "entry_q_start")),
+                                          _ptr(_i32(entry_q_len, "entry_q_len")), _ptr(_i32(entry_slot, "entry_slot")),
+                                          c_int(n_entries), c_int(channels), _stream()))
+
+
+def diff_attention_generic(q, out, k_cache, v_cache, block_table, tok_entry, positions, H: int, G: int, D: int,
+                           V: int, page_size: int, window: Optional[int], scale: float, lam: float, eps: float,
+                           out_scale: float) -> None:
+    """One warp per (token, head): two causal softmaxes over the same values, a1 - lam a2, weightless RMS
+    norm over V, times out_scale.  q [T, H*2*D], out [T, H*V], caches of q's dtype."""
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_cache.dtype == v_cache.dtype
+    _check(lib().infero_diff_attention_generic(
+        _ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)), _ptr(k_cache), _ptr(v_cache), c_int(_dt(q)),
+        _ptr(_i32(block_table, "block_table")), c_int(block_table.shape[1]), _ptr(_i32(tok_entry, "tok_entry")),
+        _ptr(_i32(positions, "positions")), c_int(T), c_int(H), c_int(G), c_int(D), c_int(V), c_int(page_size),
+        c_int(window or 0), c_float(scale), c_float(lam), c_float(eps), c_float(out_scale), _stream()))
+
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, shared_gate: Optional[torch.Tensor], top: int):
+    """(top_idx int32 [T, top], top_w float32 [T, top], gate float32 [T] or None); see csrc/moe.cu."""
+    T, d = h.shape
+    E = router.shape[0]
+    assert h.stride(1) == 1 and router.dtype == h.dtype and router.is_contiguous() and router.shape[1] == d
+    idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
+    w = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    gate = None
+    if shared_gate is not None:
+        assert shared_gate.dtype == h.dtype and shared_gate.numel() == d and shared_gate.is_contiguous()
+        gate = torch.empty(T, dtype=torch.float32, device=h.device)
+    _check(lib().infero_moe_route(_ptr(h), c_int(h.stride(0)), _ptr(router), _ptr(shared_gate), c_int(_dt(h)),
+                                  _ptr(idx), _ptr(w), _ptr(gate), c_int(T), c_int(d), c_int(E), c_int(top), _stream()))
+    return idx, w, gate
+
+
+def moe_experts_streamed(h, gate_up, down, top_idx, top_w, shared, shared_gate, y) -> None:
+    """y[t] = sum_c top_w[t, c] * expert_{top_idx[t, c]}(h[t]) (+ shared_gate[t] * shared[t]); every (token,
+    choice) streams its expert's rows.  gate_up [E, 2 ff, d] (rows alternate gate_j, up_j), down [E, d, ff]."""
+    T, d = h.shape
+    E, ff2, _ = gate_up.shape
+    ff, top = ff2 // 2, top_idx.shape[1]
+    assert gate_up.dtype == h.dtype == down.dtype and gate_up.is_contiguous() and down.is_contiguous()
+    assert tuple(down.shape) == (E, d, ff) and y.dtype == torch.float32 and y.is_contiguous() and y.shape == (T, d)
+    act = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
+    _check(lib().infero_moe_experts_streamed(_ptr(h), c_int(h.stride(0)), _ptr(gate_up), _ptr(down), c_int(_dt(h)),
+                                             _ptr(_i32(top_idx, "top_idx")), _ptr(_f32(top_w, "top_w")),
+                                             _ptr(_f32(shared, "shared")), _ptr(_f32(shared_gate, "shared_gate")),
+                                             _ptr(act), _ptr(y), c_int(T), c_int(d), c_int(ff), c_int(top), _stream()))

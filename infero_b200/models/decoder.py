@@ -124,6 +124,7 @@ class DecoderModel:
             # into its own last product when that block is of its kind)
             nxt = s.schedule[i + 1] if i + 1 < len(s.schedule) else None
             ctx.upcoming = (self.blocks[nxt.block], nxt) if nxt is not None else None
+            ctx.schedule_index = i
             delta = self.blocks[entry.block].forward(ctx, x, delta, entry)
         ctx.upcoming = None
         if logit_rows is None or logit_rows.numel() == 0:

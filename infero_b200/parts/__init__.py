@@ -3,17 +3,27 @@ from ..registry import register_part
 from .base import (FeedForward, KvCacheSpec, Mixer, Norm, Part, PositionEncoding, StateSpec,
                    TensorDecl)
 from .linear import Linear
-from .norm import RmsNorm
-from .rope import RopeNeox
+from .norm import RmsNorm, ScalarRmsNorm
+from .rope import RopeInterleaved, RopeNeox
 from .mlp import SwiGluMlp
 from .attention import GqaAttention
-from .block import PreNormBlock
+from .hgrn2 import Hgrn2Mixer
+from .diff_attention import DiffAttention
+from .moe import MoeSwiGlu
+from .block import GatedPostNormBlock, PreNormBlock
 
 register_part("norm", "rmsnorm", RmsNorm)
 register_part("position", "rope_neox", RopeNeox)
 register_part("feed_forward", "swiglu", SwiGluMlp)
 register_part("mixer", "gqa_attention", GqaAttention)
 register_part("block", "prenorm", PreNormBlock)
+register_part("norm", "rmsnorm_scalar", ScalarRmsNorm)
+register_part("position", "rope_interleaved", RopeInterleaved)
+register_part("mixer", "hgrn2", Hgrn2Mixer)
+register_part("mixer", "diff_attention", DiffAttention)
+register_part("feed_forward", "moe_swiglu", MoeSwiGlu)
+register_part("block", "gated_postnorm", GatedPostNormBlock)
 
 __all__ = ["FeedForward", "KvCacheSpec", "Mixer", "Norm", "Part", "PositionEncoding", "StateSpec",
-           "TensorDecl", "Linear", "RmsNorm", "RopeNeox", "SwiGluMlp", "GqaAttention", "PreNormBlock"]
+           "TensorDecl", "Linear", "RmsNorm", "ScalarRmsNorm", "RopeNeox", "RopeInterleaved", "SwiGluMlp", "GqaAttention",
+           "Hgrn2Mixer", "DiffAttention", "MoeSwiGlu", "PreNormBlock", "GatedPostNormBlock"]

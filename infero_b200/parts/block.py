@@ -62,3 +62,97 @@ class PreNormBlock(Part):
         a = self.mixer.forward(ctx, h, slot)
         h = self.ffn_norm.forward(ctx, x, a)
         return self.ffn.forward(ctx, h)
+
+
+class GatedPostNormBlock(Part):
+    """The sublayers read the residual stream itself; the norm sits on their result, behind a gate:
+
+        x += norm1(mixer(x) * sigmoid(G1 x + b1));   x += norm2(ffn(x) * sigmoid(G2 x + b2))
+
+    with norms of kind "rmsnorm_scalar" (one stored number).  A gate is there where the spec names it, and the
+    feed-forward half where the spec has one.  x is float32; on the bf16 path the kernel that adds a
+    sublayer's normed result also leaves the new x in bf16 for the next sublayer's products, and the first
+    block of a run converts x once.  The block adds what a block before left pending and leaves nothing
+    pending itself."""
+
+    def __init__(self, spec: BlockSpec):
+        from .linear import Linear  # noqa: F401
+        self.spec = spec
+        p = spec.prefix
+        self.mixer_norm = part_class("norm", spec.mixer_norm.kind)(spec.mixer_norm, f"{p}.{spec.mixer_norm_name}")
+        self.mixer = part_class("mixer", spec.mixer.kind)(spec.mixer, p)
+        self.ffn = self.ffn_norm = None
+        if spec.ffn is not None:
+            self.ffn_norm = part_class("norm", spec.ffn_norm.kind)(spec.ffn_norm, f"{p}.{spec.ffn_norm_name}")
+            self.ffn = part_class("feed_forward", spec.ffn.kind)(spec.ffn, p)
+        for n in (self.mixer_norm, self.ffn_norm):
+            if n is not None and not hasattr(n, "scalar"):
+                raise ValueError("a gated post-norm block takes norms with a single stored number")
+        self.gates = [None, None]            # Linear of each half's gate
+        self.gate_bias = [None, None]
+
+    def parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None]
+
+    def _gate_names(self):
+        s = self.spec
+        return [s.mixer_gate_name, s.ffn_gate_name if self.ffn is not None else None]
+
+    def declare(self) -> List[TensorDecl]:
+        out: List[TensorDecl] = []
+        for part in self.parts():
+            out += part.declare()
+        d = self.spec.mixer.hidden
+        for name in self._gate_names():
+            if name:
+                out += [TensorDecl(f"{self.spec.prefix}.{name}", (d, d)),
+                        TensorDecl(f"{self.spec.prefix}.{name}{self.spec.gate_bias_suffix}", (d,), role="bias")]
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        from .linear import Linear
+        for part in self.parts():
+            part.bind(tensors)
+        for i, name in enumerate(self._gate_names()):
+            if name:
+                full = f"{self.spec.prefix}.{name}"
+                self.gates[i] = Linear(tensors[full], None, full)
+                self.gate_bias[i] = tensors[full + self.spec.gate_bias_suffix].float().contiguous()
+
+    def _input(self, ctx, x):
+        """x in the type the products take: x itself in 32-bit, else its bf16 copy (left by the block before
+        if that was of this kind, made here otherwise)."""
+        if ctx.act_dtype == torch.float32:
+            return x
+        from ..kernels import layer_ops as L
+        left = getattr(ctx, "_resid_act", None)
+        if left is not None and left[0] == getattr(ctx, "schedule_index", -2) - 1 and left[1].shape == x.shape:
+            return left[1]
+        h = torch.empty(x.shape, dtype=ctx.act_dtype, device=x.device)
+        L.cast_rows(x, h)
+        return h
+
+    def _half(self, ctx, x, h, y, i, norm):
+        from ..kernels import layer_ops as L
+        g = self.gates[i].forward(h, out_dtype=torch.float32) if self.gates[i] is not None else None
+        h_next = torch.empty(x.shape, dtype=ctx.act_dtype, device=x.device) if ctx.act_dtype != torch.float32 else None
+        L.gated_scalar_norm_add(x, y, g, self.gate_bias[i], norm.scalar, norm.spec.eps, h_next)
+        return x if h_next is None else h_next
+
+    def forward(self, ctx, x, delta, slot):
+        from .. import kernels as K
+        if delta is not None:
+            if hasattr(delta, "as_partials"):
+                delta = delta.as_partials()
+            if isinstance(delta, K.Partials):
+                delta = delta.materialize(torch.float32)
+            K.residual_add(x, delta.contiguous())
+            ctx._resid_act = None
+        h = self._input(ctx, x)
+        y = self.mixer.forward(ctx, h, slot)
+        h = self._half(ctx, x, h, y, 0, self.mixer_norm)
+        if self.ffn is not None:
+            y = self.ffn.forward(ctx, h)
+            h = self._half(ctx, x, h, y, 1, self.ffn_norm)
+        ctx._resid_act = (getattr(ctx, "schedule_index", -2), h)
+        return None

@@ -29,7 +29,7 @@ class SwiGluMlp(FeedForward):
         self.stored_stacked = "gate_up" in self.names    # the checkpoint holds one [gate; up] tensor
 
     def _n(self, role: str) -> str:
-        return f"{self.prefix}.{self.names[role]}.weight"
+        return f"{self.prefix}.{self.names[role]}{self.spec.weight_suffix}"
 
     def declare(self) -> List[TensorDecl]:
         d, ff = self.spec.hidden, self.spec.intermediate

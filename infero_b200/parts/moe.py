@@ -1,0 +1,77 @@
+"""Mixture-of-experts feed-forward with SwiGLU experts and an optional shared expert."""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import kernels as K
+from ..config.spec import FeedForwardSpec
+from ..kernels import layer_ops as L
+from .base import FeedForward, TensorDecl
+from .mlp import SwiGluMlp
+
+
+class MoeSwiGlu(FeedForward):
+    """z = Wr h in 32-bit; the ``top`` experts with the largest logits, weights = softmax over those logits
+    alone; delta = sum_c w_c * down_e(silu(gate_e h) * up_e h).  A shared expert of the same form (width
+    ``shared_intermediate``) runs for every token and is added times sigmoid(w_sg . h).
+
+    The experts' matrices are stacked when the weights are bound: gate and up as [E, 2 ff, d] with rows
+    alternating gate_j, up_j (the layout of the package's SwiGLU products), down as [E, d, ff]."""
+
+    def __init__(self, spec: FeedForwardSpec, prefix: str):
+        self.spec, self.prefix = spec, prefix
+        self.E, self.top, self.ff = int(spec.experts), int(spec.top), int(spec.intermediate)
+        self.names = spec.tensor_names()
+        self.shared: Optional[SwiGluMlp] = None
+        if spec.shared_intermediate > 0:
+            sh = self.names["shared"]
+            sub = FeedForwardSpec(kind="swiglu", hidden=spec.hidden, intermediate=spec.shared_intermediate,
+                                  names=tuple((r, f"{sh}.{self.names[r]}") for r in ("gate", "up", "down")),
+                                  weight_suffix=spec.weight_suffix)
+            self.shared = SwiGluMlp(sub, prefix)
+
+    def _expert(self, e: int, role: str) -> str:
+        return f"{self.prefix}.{self.names['expert'].format(e)}.{self.names[role]}{self.spec.weight_suffix}"
+
+    def _n(self, role: str) -> str:
+        return f"{self.prefix}.{self.names[role]}{self.spec.weight_suffix}"
+
+    def declare(self) -> List[TensorDecl]:
+        d, ff = self.spec.hidden, self.ff
+        out: List[TensorDecl] = []
+        for e in range(self.E):
+            out += [TensorDecl(self._expert(e, "gate"), (ff, d)), TensorDecl(self._expert(e, "up"), (ff, d)),
+                    TensorDecl(self._expert(e, "down"), (d, ff))]
+        out.append(TensorDecl(self._n("router"), (self.E, d)))
+        if self.shared is not None:
+            out += self.shared.declare()
+            out.append(TensorDecl(self._n("shared_gate"), (1, d)))
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        g = torch.stack([tensors[self._expert(e, "gate")] for e in range(self.E)])
+        u = torch.stack([tensors[self._expert(e, "up")] for e in range(self.E)])
+        self.gate_up = torch.stack([g, u], dim=2).reshape(self.E, 2 * self.ff, self.spec.hidden).contiguous()
+        self.down = torch.stack([tensors[self._expert(e, "down")] for e in range(self.E)]).contiguous()
+        self.router = tensors[self._n("router")].contiguous()
+        self.shared_gate = None
+        if self.shared is not None:
+            self.shared.bind(tensors)
+            self.shared_gate = tensors[self._n("shared_gate")].reshape(-1).contiguous()
+
+    def forward(self, ctx, h):
+        T, d = h.shape
+        idx, w, gate = L.moe_route(h, self.router, self.shared_gate, self.top)
+        shared = None
+        if self.shared is not None:
+            shared = self.shared.forward(ctx, h)
+            if isinstance(shared, K.Partials):
+                shared = shared.materialize(torch.float32)
+            elif shared.dtype != torch.float32:
+                shared = shared.float()
+        y = torch.empty((T, d), dtype=torch.float32, device=h.device)
+        from ..kernels import moe as M
+        M.experts(h, self.gate_up, self.down, idx, w, shared, gate, y)
+        return y

@@ -30,3 +30,20 @@ class RmsNorm(Norm):
         out = torch.empty((n, self.spec.dim), dtype=ctx.act_dtype, device=x.device)
         K.add_rmsnorm(x, delta, self.weight, self.spec.eps, out, rows)
         return out
+
+
+class ScalarRmsNorm(RmsNorm):
+    """x * rsqrt(mean(x^2) + eps) * g with g a single stored number.  ``scalar`` is that number as a
+    float32 tensor of one element (what kernels that normalise a sublayer's result take); ``weight`` is
+    it repeated over the coordinates, which the shared norm kernel takes."""
+
+    def __init__(self, spec: NormSpec, weight_name: str):
+        super().__init__(spec, weight_name)
+        self.scalar: Optional[torch.Tensor] = None
+
+    def declare(self) -> List[TensorDecl]:
+        return [TensorDecl(self.weight_name, (), role="norm", init="ones")]
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.scalar = tensors[self.weight_name].reshape(1).float().contiguous()
+        self.weight = self.scalar.expand(self.spec.dim).contiguous()

@@ -27,3 +27,9 @@ class RopeNeox(PositionEncoding):
         if key not in self._inv_dev:
             self._inv_dev[key] = self._inv_host.to(device)
         return self._inv_dev[key]
+
+
+class RopeInterleaved(RopeNeox):
+    """The same angles on adjacent pairs: dimension 2i turns with dimension 2i + 1.  Mixers whose kernels
+    take the pairing as a parameter ask ``pairing``; the table is the one of the base class."""
+    pairing = "adjacent"

@@ -45,7 +45,9 @@ def architectures() -> Dict[str, Architecture]:
 
 def resolve_architecture(raw: Dict[str, Any]) -> Architecture:
     """Pick the architecture for a config.json dict: ``architectures[0]``, else ``model_type``."""
-    names = raw.get("architectures") or []
+    names = list(raw.get("architectures") or [])
+    if isinstance(raw.get("architecture"), str):       # some configurations name their one architecture so
+        names.append(raw["architecture"])
     for n in names:
         if n in _ARCHITECTURES:
             return _ARCHITECTURES[n]
@@ -87,6 +89,8 @@ def _register_builtin() -> None:
     from .config.qwen2 import Qwen2Config
     register_architecture("Qwen2ForCausalLM", Qwen2Config.from_dict,
                           lambda c: c.to_model_spec(), model_types=("qwen2",))
+    from .config.vufizen import VufizenConfig
+    register_architecture("Vufizen", VufizenConfig.from_dict, lambda c: c.to_model_spec())
 
 
 _register_builtin()
