@@ -107,24 +107,26 @@ __device__ __forceinline__ void load_q(uint32_t (*qf)[4], const bf16* base, size
 // o += p v.  k_tile/v_tile hold the slice at rows [row0, row0 + 16).
 //   key_base: absolute position of row row0;  lo/hi0/hi1: visible keys are lo0 <= j <= hi for
 //   the thread's two rows (g and g + 8).
-template <int D, typename Layout = PaddedRows<D>>
-__device__ __forceinline__ void slice16(const uint32_t (*qf)[4], const bf16* k_tile, const bf16* v_tile, int row0,
-                                        int key_base, int lo0, int hi0, int lo1, int hi1, float scale_log2,
-                                        float* m, float* l, float (*o)[4], int lane) {
+//   Keys are DK wide and values DV wide; the key's columns start at 16-byte chunk `kchunk0` of its tile row
+//   (a tile row may hold several keys side by side).
+template <int DK, int DV, typename KLayout, typename VLayout>
+__device__ __forceinline__ void slice16_kv(const uint32_t (*qf)[4], const bf16* k_tile, const bf16* v_tile, int row0,
+                                           int key_base, int lo0, int hi0, int lo1, int hi1, float scale_log2,
+                                           float* m, float* l, float (*o)[4], int lane, int kchunk0 = 0) {
     const int c = lane & 3;
     float s[2][4];
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
-    // ---- s = q k^T: two n-tiles of 8 keys, D/16 k-steps; one ldmatrix.x4 per k-step ----------
+    // ---- s = q k^T: two n-tiles of 8 keys, DK/16 k-steps; one ldmatrix.x4 per k-step ----------
     {
         const int mi = lane >> 3;                     // matrix this lane addresses
         const int krow = row0 + (mi >> 1) * 8 + (lane & 7);
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
+        for (int ks = 0; ks < DK / 16; ++ks) {
             uint32_t b[4];
-            ldmatrix_x4(b, smem_addr(k_tile + (size_t)Layout::chunk(krow, ks * 2 + (mi & 1)) * 8));
+            ldmatrix_x4(b, smem_addr(k_tile + (size_t)KLayout::chunk(krow, kchunk0 + ks * 2 + (mi & 1)) * 8));
             mma16816(s[0], qf[ks], b[0], b[1]);
             mma16816(s[1], qf[ks], b[2], b[3]);
         }
@@ -174,14 +176,14 @@ __device__ __forceinline__ void slice16(const uint32_t (*qf)[4], const bf16* k_t
     }
     l[0] = l[0] * corr0 + sum0;        // per-thread partial sums; lanes are added up at the end
     l[1] = l[1] * corr1 + sum1;
-    // ---- o = o * corr + p v: D/8 n-tiles, one k-step of 16 keys ------------------------------
+    // ---- o = o * corr + p v: DV/8 n-tiles, one k-step of 16 keys ------------------------------
     {
         const int mi = lane >> 3;
         const int vrow = row0 + (mi & 1) * 8 + (lane & 7);
 #pragma unroll
-        for (int np = 0; np < D / 16; ++np) {
+        for (int np = 0; np < DV / 16; ++np) {
             uint32_t b[4];
-            ldmatrix_x4_trans(b, smem_addr(v_tile + (size_t)Layout::chunk(vrow, np * 2 + (mi >> 1)) * 8));
+            ldmatrix_x4_trans(b, smem_addr(v_tile + (size_t)VLayout::chunk(vrow, np * 2 + (mi >> 1)) * 8));
             float* o0 = o[np * 2];
             float* o1 = o[np * 2 + 1];
             o0[0] *= corr0; o0[1] *= corr0; o0[2] *= corr1; o0[3] *= corr1;
@@ -190,6 +192,13 @@ __device__ __forceinline__ void slice16(const uint32_t (*qf)[4], const bf16* k_t
             mma16816(o1, pf, b[2], b[3]);
         }
     }
+}
+
+template <int D, typename Layout = PaddedRows<D>>
+__device__ __forceinline__ void slice16(const uint32_t (*qf)[4], const bf16* k_tile, const bf16* v_tile, int row0,
+                                        int key_base, int lo0, int hi0, int lo1, int hi1, float scale_log2,
+                                        float* m, float* l, float (*o)[4], int lane) {
+    slice16_kv<D, D, Layout, Layout>(qf, k_tile, v_tile, row0, key_base, lo0, hi0, lo1, hi1, scale_log2, m, l, o, lane);
 }
 
 }  // namespace attn

@@ -132,3 +132,25 @@ def moe_experts_streamed(h, gate_up, down, top_idx, top_w, shared, shared_gate, 
                                              _ptr(_i32(top_idx, "top_idx")), _ptr(_f32(top_w, "top_w")),
                                              _ptr(_f32(shared, "shared")), _ptr(_f32(shared_gate, "shared_gate")),
                                              _ptr(act), _ptr(y), c_int(T), c_int(d), c_int(ff), c_int(top), _stream()))
+
+
+def moe_experts_grouped(h, gate_up, down, top_idx, top_w, shared, shared_gate, y) -> None:
+    """The same result as ``moe_experts_streamed`` by grouped tensor-core products (bf16): the (token, choice)
+    pairs are sorted by expert into 64-row tiles; see csrc/moe_grouped.cu."""
+    T, d = h.shape
+    E, ff2, _ = gate_up.shape
+    ff, top = ff2 // 2, top_idx.shape[1]
+    assert h.dtype == torch.bfloat16 and gate_up.dtype == torch.bfloat16 and down.dtype == torch.bfloat16
+    assert gate_up.is_contiguous() and down.is_contiguous() and tuple(down.shape) == (E, d, ff)
+    assert y.dtype == torch.float32 and y.is_contiguous() and y.shape == (T, d) and h.stride(1) == 1
+    tiles = int(lib().infero_moe_grouped_tiles(c_int(T * top), c_int(E)))
+    dev = h.device
+    ints = torch.empty(2 * tiles * 64 + tiles, dtype=torch.int32, device=dev)
+    sorted_pair, a_rows, tile_expert = ints[:tiles * 64], ints[tiles * 64:2 * tiles * 64], ints[2 * tiles * 64:]
+    act = torch.empty((tiles * 64, ff), dtype=torch.bfloat16, device=dev)
+    part = torch.empty((T * top, d), dtype=torch.float32, device=dev)
+    _check(lib().infero_moe_experts_grouped(_ptr(h), c_int(h.stride(0)), _ptr(gate_up), _ptr(down),
+                                            _ptr(_i32(top_idx, "top_idx")), _ptr(_f32(top_w, "top_w")),
+                                            _ptr(_f32(shared, "shared")), _ptr(_f32(shared_gate, "shared_gate")),
+                                            _ptr(sorted_pair), _ptr(a_rows), _ptr(tile_expert), _ptr(act), _ptr(part),
+                                            _ptr(y), c_int(T), c_int(d), c_int(ff), c_int(E), c_int(top), _stream()))
