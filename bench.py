@@ -283,8 +283,15 @@ def main(argv=None) -> int:
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="size of the timed prompt step (the contract's 2,048; 8,192 and more show attention over long contexts)")
+    ap.add_argument("--designs", action="store_true",
+                    help="instead of the headline workload: Vufizen beside Qwen2 at equal layer sizes, prompt and decode "
+                         "steps and the kernels alone (infero_b200/tools/design_bench.py; its own JSON line)")
+    ap.add_argument("--design-sizes", default="s,m")
     args = ap.parse_args(argv)
 
+    if args.designs and args.impl != "reference":
+        from infero_b200.tools import design_bench
+        return design_bench.main(["--sizes", args.design_sizes, "--batch", str(args.batch), "--prompt", str(args.prefill_tokens)])
     if args.impl == "reference":
         print(json.dumps({"impl": "reference",
                           "unavailable": "jackwangfeng/infero is a Rust workspace (no setup.py / pyproject.toml; "

@@ -9,11 +9,20 @@
 // the steps before left in the request's slot, and leaves the state behind; a step of one token is
 // the same walk of length one.  Thread (j, s) keeps rows s*DPT .. s*DPT+DPT-1 of column j of S in
 // registers; tokens are staged eight at a time in shared memory with the activations applied once.
+//
+// A long portion (LONG tokens and more) is cut into chunks of CHUNK tokens that run side by side, in three
+// launches, because the recurrence is linear in S: (1) every chunk walks its tokens from a zero state and keeps
+// its end state L_c and the product P_c of its forget gates; (2) one block per (head, request) strings them
+// together, S_(c+1) = diag(P_c) S_c + L_c from the request's state, leaving every chunk's start state where L_c
+// was; (3) every chunk walks its tokens again from its start state and writes the results.  Whether a request
+// goes that way depends on its own portion alone, so what is computed for it does not depend on the batch.
 #include "common.cuh"
 
 namespace {
 
 constexpr int TT = 8;      // tokens staged per round
+constexpr int CHUNK = 128, LONG = 512;
+enum { WHOLE = 0, LOCAL = 1, FROM_START = 2 };
 
 template <typename T, int DPT>
 __global__ void __launch_bounds__(512)
@@ -22,22 +31,41 @@ hgrn2_scan_kernel(const float* __restrict__ proj, int stride, int q_off, int f_o
                   const float* __restrict__ out_w, float eps, float* __restrict__ state,
                   const int* __restrict__ entry_q_start, const int* __restrict__ entry_q_len,
                   const int* __restrict__ entry_slot, T* __restrict__ out, int out_stride,
-                  int H, int D, int V, int DS) {
+                  int H, int D, int V, int DS, int mode, float* __restrict__ chunk_state, float* __restrict__ chunk_decay,
+                  const int* __restrict__ entry_chunk0) {
     extern __shared__ float sm[];
     float* qs = sm;                      // [TT][D]
     float* fs = qs + TT * D;             // [TT][D]
     float* vs = fs + TT * D;             // [TT][V]
     float* part = vs + TT * V;           // [TT][DS][V]
     const int h = blockIdx.x, e = blockIdx.y;
-    const int row0 = entry_q_start[e], n = entry_q_len[e], slot = entry_slot[e];
+    int row0 = entry_q_start[e], n = entry_q_len[e];
+    const int slot = entry_slot[e];
+    const bool is_long = n >= LONG;
+    if ((mode == WHOLE) == is_long) return;                 // long portions go by chunks, the others whole
+    float* st_chunk = nullptr;
+    float* decay = nullptr;
+    if (mode != WHOLE) {
+        const int c = blockIdx.z;
+        if (c * CHUNK >= n) return;
+        const size_t ci = (size_t)entry_chunk0[e] + c;
+        st_chunk = chunk_state + (ci * H + blockIdx.x) * D * V;
+        decay = chunk_decay + (ci * H + blockIdx.x) * D;
+        row0 += c * CHUNK;
+        n = min(CHUNK, n - c * CHUNK);
+    }
     const int tid = threadIdx.x, nthreads = blockDim.x;
     const int j = tid % V, s = tid / V;
     const bool active = s < DS;
     const int i0 = s * DPT;
     float S[DPT];
-    float* st = state + (((size_t)slot * H + h) * D) * V;
+    float* st = mode == WHOLE ? state + (((size_t)slot * H + h) * D) * V : st_chunk;
+    float P[DPT];                                            // product of the forget gates (LOCAL, threads of column 0)
 #pragma unroll
-    for (int ii = 0; ii < DPT; ++ii) S[ii] = (active && i0 + ii < D) ? st[(size_t)(i0 + ii) * V + j] : 0.f;
+    for (int ii = 0; ii < DPT; ++ii) {
+        S[ii] = (mode != LOCAL && active && i0 + ii < D) ? st[(size_t)(i0 + ii) * V + j] : 0.f;
+        P[ii] = 1.f;
+    }
     const int lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
     for (int t0 = 0; t0 < n; t0 += TT) {
         const int nt = min(TT, n - t0);
@@ -66,12 +94,14 @@ hgrn2_scan_kernel(const float* __restrict__ proj, int stride, int q_off, int f_o
                         const float f = fs[tt * D + i0 + ii];
                         S[ii] = fmaf(f, S[ii], (1.0f - f) * vj);
                         o = fmaf(S[ii], qs[tt * D + i0 + ii], o);
+                        if (mode == LOCAL) P[ii] *= f;
                     }
                 }
                 part[(tt * DS + s) * V + j] = o;
             }
         }
         __syncthreads();
+        if (mode == LOCAL) continue;                         // only the end state is wanted
         for (int tt = warp; tt < nt; tt += nwarps) {
             float ss = 0.f;
             for (int jj = lane; jj < V; jj += 32) {
@@ -86,17 +116,45 @@ hgrn2_scan_kernel(const float* __restrict__ proj, int stride, int q_off, int f_o
             for (int jj = lane; jj < V; jj += 32) orow[jj] = from_f32<T>(part[(tt * DS) * V + jj] * r * out_w[jj]);
         }
     }
-    if (active) {
+    if (active && mode != FROM_START) {
 #pragma unroll
         for (int ii = 0; ii < DPT; ++ii)
-            if (i0 + ii < D) st[(size_t)(i0 + ii) * V + j] = S[ii];
+            if (i0 + ii < D) {
+                st[(size_t)(i0 + ii) * V + j] = S[ii];
+                if (mode == LOCAL && j == 0) decay[i0 + ii] = P[ii];
+            }
+    }
+}
+
+// S_(c+1) = diag(P_c) S_c + L_c over the chunks of every long portion; chunk_state[c] becomes S_c.
+__global__ void hgrn2_chain_kernel(float* __restrict__ state, float* __restrict__ chunk_state,
+                                   const float* __restrict__ chunk_decay, const int* __restrict__ entry_q_len,
+                                   const int* __restrict__ entry_slot, const int* __restrict__ entry_chunk0,
+                                   int H, int D, int V) {
+    const int h = blockIdx.x, e = blockIdx.y;
+    const int n = entry_q_len[e];
+    if (n < LONG) return;
+    const int chunks = (n + CHUNK - 1) / CHUNK;
+    float* st = state + (((size_t)entry_slot[e] * H + h) * D) * V;
+    for (int idx = threadIdx.x; idx < D * V; idx += blockDim.x) {
+        const int i = idx / V;
+        float S = st[idx];
+        for (int c = 0; c < chunks; ++c) {
+            const size_t ci = (size_t)entry_chunk0[e] + c;
+            float* L = chunk_state + (ci * H + h) * D * V;
+            const float l = L[idx];
+            L[idx] = S;
+            S = fmaf(chunk_decay[(ci * H + h) * D + i], S, l);
+        }
+        st[idx] = S;
     }
 }
 
 template <typename T, int DPT>
 int launch(const float* proj, int stride, int q_off, int f_off, int v_off, const float* f_bias, const float* lower,
            const float* out_w, float eps, float* state, const int* qs, const int* ql, const int* es, void* out,
-           int out_stride, int E, int H, int D, int V, cudaStream_t stream) {
+           int out_stride, int E, int H, int D, int V, int max_chunks, float* chunk_state, float* chunk_decay,
+           const int* entry_chunk0, int any_short, cudaStream_t stream) {
     const int DS = (D + DPT - 1) / DPT;
     const int threads = ((V * DS + 31) / 32) * 32;
     const size_t smem = (size_t)TT * (2 * D + V + DS * V) * sizeof(float);
@@ -105,8 +163,16 @@ int launch(const float* proj, int stride, int q_off, int f_off, int v_off, const
         INFERO_REQUIRE(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess,
                        "hgrn2: %zu bytes of shared memory are not available", smem);
     }
-    kern<<<dim3(H, E), threads, smem, stream>>>(proj, stride, q_off, f_off, v_off, f_bias, lower, out_w, eps, state,
-                                                qs, ql, es, (T*)out, out_stride, H, D, V, DS);
+    if (any_short)
+        kern<<<dim3(H, E), threads, smem, stream>>>(proj, stride, q_off, f_off, v_off, f_bias, lower, out_w, eps, state,
+                                                    qs, ql, es, (T*)out, out_stride, H, D, V, DS, WHOLE, nullptr, nullptr, nullptr);
+    if (max_chunks > 0) {
+        kern<<<dim3(H, E, max_chunks), threads, smem, stream>>>(proj, stride, q_off, f_off, v_off, f_bias, lower, out_w, eps,
+            state, qs, ql, es, (T*)out, out_stride, H, D, V, DS, LOCAL, chunk_state, chunk_decay, entry_chunk0);
+        hgrn2_chain_kernel<<<dim3(H, E), 256, 0, stream>>>(state, chunk_state, chunk_decay, ql, es, entry_chunk0, H, D, V);
+        kern<<<dim3(H, E, max_chunks), threads, smem, stream>>>(proj, stride, q_off, f_off, v_off, f_bias, lower, out_w, eps,
+            state, qs, ql, es, (T*)out, out_stride, H, D, V, DS, FROM_START, chunk_state, chunk_decay, entry_chunk0);
+    }
     return infero_check_launch("hgrn2_scan");
 }
 
@@ -114,19 +180,27 @@ int launch(const float* proj, int stride, int q_off, int f_off, int v_off, const
 
 extern "C" {
 
+int infero_hgrn2_chunk() { return CHUNK; }
+int infero_hgrn2_long() { return LONG; }
+
 // proj: float32 [tokens, stride] holding q' at column q_off (H*D), f' at f_off (H*D), v at v_off (H*V).
 // state: float32 [slots, H, D, V].  out: [tokens, H*V] of out_dtype.
+// Portions of infero_hgrn2_long() tokens and more run by chunks of infero_hgrn2_chunk(): max_chunks is the largest
+// chunk count of any such portion (0: there is none), entry_chunk0[e] the first chunk index of entry e in
+// chunk_state float32 [chunks, H, D, V] and chunk_decay float32 [chunks, H, D]; any_short: some portion is shorter.
 int infero_hgrn2_scan(const float* proj, int stride, int q_off, int f_off, int v_off, const float* f_bias,
                       const float* lower, const float* out_w, float eps, float* state, const int* entry_q_start,
                       const int* entry_q_len, const int* entry_slot, void* out, int out_dtype, int out_stride,
-                      int n_entries, int H, int D, int V, cudaStream_t stream) {
+                      int n_entries, int H, int D, int V, int max_chunks, float* chunk_state, float* chunk_decay,
+                      const int* entry_chunk0, int any_short, cudaStream_t stream) {
     if (n_entries == 0) return 0;
     INFERO_REQUIRE(H > 0 && D > 0 && V > 0 && V <= 512, "hgrn2: bad sizes H=%d D=%d V=%d", H, D, V);
     int dpt = 8;
     while (dpt < 32 && V * ((D + dpt - 1) / dpt) > 512) dpt *= 2;
     INFERO_REQUIRE(V * ((D + dpt - 1) / dpt) <= 512, "hgrn2: a state of %d x %d per head is too large", D, V);
 #define GO(TY, N) return launch<TY, N>(proj, stride, q_off, f_off, v_off, f_bias, lower, out_w, eps, state, \
-                                       entry_q_start, entry_q_len, entry_slot, out, out_stride, n_entries, H, D, V, stream)
+                                       entry_q_start, entry_q_len, entry_slot, out, out_stride, n_entries, H, D, V, max_chunks, chunk_state, \
+                                       chunk_decay, entry_chunk0, any_short, stream)
     if (out_dtype == INFERO_F32) {
         if (dpt == 8) GO(float, 8); if (dpt == 16) GO(float, 16); GO(float, 32);
     } else {

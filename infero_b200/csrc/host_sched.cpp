@@ -207,7 +207,8 @@ int infero_sched_plan(void* h, int* out, int cap) {
         const int slack = (P - filled % P) % P;                    // free rows in its last page
         int min_left = G ? left(0) : 0;
         for (int g = 1; g < G; ++g) min_left = std::min(min_left, left(g));
-        const long long room = slack + (long long)std::max(0, min_left) * P;
+        // (a model that keeps no paged keys at all, only per-request state, is never short of pages)
+        const long long room = G ? slack + (long long)std::max(0, min_left) * P : (long long)remaining;
         long long cnt = std::min<long long>(std::min(remaining, budget), room);
         if (s->max_prefill_chunk > 0) cnt = std::min<long long>(cnt, s->max_prefill_chunk);
         if (cnt <= 0) continue;

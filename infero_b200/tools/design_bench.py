@@ -1,0 +1,282 @@
+"""Vufizen beside Qwen2 at equal layer sizes: whole prompt steps and decode steps, and the designs' own kernels
+one by one against their rooflines.
+
+    python -m infero_b200.tools.design_bench [--sizes s,m] [--prompt 2048] [--context 2048] [--batch 8] [--layers 8]
+
+(also ``bench.py --designs``).  Random weights made on the device, bf16.  Per size two models of the same width
+and depth: Vufizen (HGRN2 and differential-attention layers alternating, routed experts with a shared one) and
+Qwen2 with the same head count, a head as wide as both maps together, and a feed-forward as wide as what one token
+uses of the experts.  Steps are timed with CUDA events after warm-up, an L2 flush between timed steps; kernels are
+timed alone the same way.  One JSON line at the end.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import random
+import sys
+import types
+
+SIZES = {
+    "s": dict(width=1024, heads=8, kv=2, dim=64, vdim=128, experts=16, top=4, ff=512, shared=1024, vocab=32000),
+    "m": dict(width=2048, heads=16, kv=4, dim=64, vdim=128, experts=32, top=4, ff=768, shared=1536, vocab=32000),
+    "l": dict(width=4096, heads=32, kv=8, dim=64, vdim=128, experts=64, top=8, ff=768, shared=2048, vocab=32000),
+}
+
+
+def vufizen_config(z, layers):
+    mlp = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["ff"]},
+           "shared": {"ff": z["shared"]}}
+    att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["vdim"], "conv": 4, "diff": 0.5,
+           "rot": {"base": 10000.0, "dims": z["dim"]}, "scale": z["dim"] ** -0.5}
+    hg = {"heads": z["heads"], "dim": z["dim"], "vdim": z["vdim"]}
+    return {"architecture": "Vufizen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+            "layers": [{"type": "hgrn2" if i % 2 == 0 else "attention", "mixer": hg if i % 2 == 0 else att, "mlp": mlp}
+                       for i in range(layers)]}
+
+
+def qwen2_config(z, layers):
+    return {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": layers,
+            "hidden_size": z["width"], "num_attention_heads": z["heads"], "num_key_value_heads": z["kv"],
+            "head_dim": 2 * z["dim"], "intermediate_size": z["top"] * z["ff"] + z["shared"], "vocab_size": z["vocab"],
+            "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False}
+
+
+class _Timer:
+    def __init__(self):
+        import torch
+        self.torch = torch
+        self.flush = torch.empty(192 << 20, dtype=torch.uint8, device="cuda")
+
+    def __call__(self, fn, reps=7, warmup=3, setup=None):
+        torch = self.torch
+        times = []
+        for i in range(warmup + reps):
+            if setup:
+                setup()
+            self.flush.fill_(i & 255)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= warmup:
+                times.append(e0.elapsed_time(e1))
+        times.sort()
+        return times[len(times) // 2]
+
+
+def time_model(cfg, prompt, context, batch, timer):
+    import torch
+    from infero_b200.config import EngineConfig
+    from infero_b200.engine import ModelRunner, StepEntry
+    from infero_b200.loading import random_model
+    model, _ = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0", generate_on_device=True)
+    vocab = model.spec.vocab_size
+    rng = random.Random(1)
+    ps = 16
+    toks = lambda n: [rng.randrange(vocab) for _ in range(n)]                   # noqa: E731
+    runner = ModelRunner(model, EngineConfig(dtype="bfloat16", page_size=ps, num_pages=2 * (-(-prompt // ps)), max_seqs=2,
+                                             ctx=prompt, max_batch_tokens=prompt, cuda_graphs=False))
+    p = toks(prompt)
+
+    def prefill():
+        runner.step([StepEntry("p", p, [prompt - 1])])
+    pre_ms = timer(prefill, setup=lambda: (("p" in runner.manager.requests) and runner.close("p"), runner.open("p")))
+    del runner
+    torch.cuda.empty_cache()
+    steps = 24
+    runner = ModelRunner(model, EngineConfig(dtype="bfloat16", page_size=ps, num_pages=batch * (-(-(context + 64) // ps)),
+                                             max_seqs=batch, ctx=context + 64, max_batch_tokens=max(2048, batch),
+                                             max_logit_rows=max(8, batch), cuda_graphs=True))
+    rids = [f"d{i}" for i in range(batch)]
+    for r in rids:
+        runner.open(r)
+        done = 0
+        while done < context - steps:
+            n = min(2048, context - steps - done)
+            runner.step([StepEntry(r, toks(n), [])])
+            done += n
+    for _ in range(4):                                     # eager, captured, replayed
+        runner.step([StepEntry(r, toks(1), [0]) for r in rids])
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps - 4):
+        runner.step([StepEntry(r, toks(1), [0]) for r in rids])
+    e1.record()
+    torch.cuda.synchronize()
+    dec_ms = e0.elapsed_time(e1) / (steps - 4)
+    out = {"prefill_tok_s": round(prompt / pre_ms * 1e3, 1), "prefill_ms": round(pre_ms, 3),
+           "decode_tok_s": round(batch / dec_ms * 1e3, 1), "decode_ms_per_step": round(dec_ms, 4),
+           "weight_mib": model.weight_bytes() >> 20, "graph_replays": runner.graph_replays}
+    del runner, model
+    torch.cuda.empty_cache()
+    return out
+
+
+def time_kernels(z, T, context, batch, timer, peaks):
+    """The new design's kernels alone, each beside the kernel of the built-in decoder that does the like job."""
+    import numpy as np
+    import torch
+    from infero_b200 import kernels as K
+    from infero_b200.kernels import attention as A, diff_attention as DA, layer_ops as L, moe as M, tc_gemm
+    dev, bf = "cuda:0", torch.bfloat16
+    d, H, G, D, V = z["width"], z["heads"], z["kv"], z["dim"], z["vdim"]
+    E, top, ff = z["experts"], z["top"], z["ff"]
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *s, dtype=bf, k=1.0: (torch.randn(s, generator=g, device=dev) * k).to(dtype)     # noqa: E731
+    i32 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=dev)                 # noqa: E731
+    hbm, tfl = peaks["hbm_gbs"], peaks["bf16_tflops"]
+    rows = {}
+
+    def note(name, ms, bytes_=0.0, flops=0.0):
+        r = {"us": round(ms * 1e3, 1)}
+        if bytes_:
+            r["gb_s"] = round(bytes_ / ms / 1e6, 1)
+            r["hbm_frac"] = round(bytes_ / ms / 1e6 / hbm, 3)
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 1)
+            r["tensor_frac"] = round(flops / ms / 1e9 / tfl, 3)
+        rows[name] = r
+
+    def batch_ctx(q_lens, pos0, ps=16):
+        E_ = len(q_lens)
+        per = [-(-(p + n) // ps) for p, n in zip(pos0, q_lens)]
+        table = torch.full((E_, max(per)), -1, dtype=torch.int32)
+        at = 0
+        for e, n in enumerate(per):
+            table[e, :n] = torch.arange(at, at + n, dtype=torch.int32)
+            at += n
+        qs = np.concatenate([[0], np.cumsum(q_lens)[:-1]])
+        ctx = types.SimpleNamespace(
+            n_entries=E_, n_tokens=int(sum(q_lens)), h_q_len=np.asarray(q_lens, dtype=np.int32), h_pos0=np.asarray(pos0, dtype=np.int32),
+            tok_entry=i32(np.repeat(np.arange(E_), q_lens)), positions=i32(np.concatenate([p + np.arange(n) for p, n in zip(pos0, q_lens)])),
+            entry_q_start=i32(qs), entry_q_len=i32(q_lens), entry_pos0=i32(pos0), entry_slot=i32(np.arange(E_)), kv_bound=None)
+        return ctx, table.to(dev), at
+
+    # ---- attention: prompt of T tokens, then `batch` single tokens at `context` -----------------------------------
+    for label, q_lens, pos0 in (("prefill", [T], [0]), ("decode", [1] * batch, [context - 1] * batch)):
+        ctx, table, pages = batch_ctx(q_lens, pos0)
+        n = ctx.n_tokens
+        kd, vd = rnd(pages, G, 16, 2 * D), rnd(pages, G, 16, V)
+        kv = types.SimpleNamespace(k=kd, v=vd, page_size=16)
+        q, out = rnd(n, 2 * H * D), torch.empty(n, H * V, dtype=bf, device=dev)
+        keys = sum(p + (n_ + 1) / 2 * 1 for p, n_ in zip(pos0, q_lens)) if label == "decode" else T / 2
+        fl = 2.0 * H * (2 * D + 2 * V) * (T * T / 2 if label == "prefill" else batch * context)
+        by = 2.0 * G * (2 * D + V) * (T if label == "prefill" else batch * context) + 2.0 * n * (2 * H * D + H * V)
+        ms = timer(lambda: DA.paged_diff_attention(ctx, q, out, kv, table, H, G, D, V, None, D ** -0.5, 0.4, 1e-5, 0.5))
+        note(f"diff_attention_{label}", ms, by, fl)
+        # the built-in attention with a head as wide as both maps (2 D) and values of the same width
+        Dq = 2 * D
+        k2, v2 = rnd(pages, G, 16, Dq), rnd(pages, G, 16, Dq)
+        q2, out2 = rnd(n, H * Dq), torch.empty(n, H * Dq, dtype=bf, device=dev)
+        fl2 = 2.0 * H * 2 * Dq * (T * T / 2 if label == "prefill" else batch * context)
+        by2 = 2.0 * G * 2 * Dq * (T if label == "prefill" else batch * context) + 4.0 * n * H * Dq
+        ms = timer(lambda: A.attention_any(q2, out2, k2, v2, table, ctx.tok_entry, ctx.positions, H, G, Dq, 16, None, Dq ** -0.5,
+                                           ctx.h_q_len, ctx.h_pos0, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_pos0))
+        note(f"gqa_attention_{label}", ms, by2, fl2)
+
+    # ---- the recurrence ------------------------------------------------------------------------------------------
+    for label, q_lens in (("prefill", [T]), ("decode", [1] * batch)):
+        ctx, _, _ = batch_ctx(q_lens, [0] * len(q_lens))
+        n = ctx.n_tokens
+        proj = rnd(n, 2 * H * D + H * V, dtype=torch.float32)
+        state = torch.zeros(len(q_lens), H, D, V, device=dev)
+        fb, lo, wn = rnd(H * D, dtype=torch.float32), torch.rand(H * D, device=dev), torch.ones(V, device=dev)
+        out = torch.empty(n, H * V, dtype=bf, device=dev)
+        ms = timer(lambda: L.hgrn2_scan(proj, 0, H * D, 2 * H * D, fb, lo, wn, 1e-5, state, ctx.entry_q_start, ctx.entry_q_len,
+                                        ctx.entry_slot, out, len(q_lens), H, D, V))
+        note(f"hgrn2_scan_{label}", ms, 4.0 * n * (2 * H * D + H * V) + 2.0 * n * H * V + 8.0 * len(q_lens) * H * D * V)
+
+    # ---- feed-forward: routed experts beside a dense SwiGLU of the width one token uses -----------------------------
+    gu, dn = rnd(E, 2 * ff, d, k=0.05), rnd(E, d, ff, k=0.05)
+    router = rnd(E, d, k=0.1)
+    dense_ff = top * ff
+    wgu, wdn = rnd(2 * dense_ff, d, k=0.05), rnd(d, dense_ff, k=0.05)
+    for label, n in (("prefill", T), ("decode", batch)):
+        h = rnd(n, d)
+        y = torch.empty(n, d, device=dev)
+        idx, w, _ = L.moe_route(h, router, None, top)
+        ms = timer(lambda: L.moe_route(h, router, None, top))
+        note(f"moe_route_{label}", ms, 2.0 * (n * d + E * d))
+        used = min(E, n * top)
+        ms = timer(lambda: M.experts(h, gu, dn, idx, w, None, None, y))
+        note(f"moe_experts_{label}", ms, 2.0 * used * 3 * ff * d + 2.0 * n * d + 4.0 * n * d, 6.0 * n * top * ff * d)
+        act = torch.empty(n, dense_ff, dtype=bf, device=dev)
+        o = torch.empty(n, d, dtype=torch.float32, device=dev)
+
+        def dense():
+            if not tc_gemm.gemm_swiglu(h, wgu, act):
+                K.swiglu(K.Partials(tc_gemm.partials(h, wgu)), act)
+            tc_gemm.gemm(act, wdn, None, o)
+        ms = timer(dense)
+        note(f"dense_swiglu_{label}", ms, 2.0 * 3 * dense_ff * d + 6.0 * n * d, 6.0 * n * dense_ff * d)
+
+    # ---- the small kernels -----------------------------------------------------------------------------------------
+    x, yv, gl = rnd(T, d, dtype=torch.float32), rnd(T, d, dtype=torch.float32), rnd(T, d, dtype=torch.float32)
+    gb, nw, hb = rnd(d, dtype=torch.float32), torch.ones(1, device=dev), torch.empty(T, d, dtype=bf, device=dev)
+    ms = timer(lambda: L.gated_scalar_norm_add(x, yv, gl, gb, nw, 1e-5, hb))
+    note("gated_norm_add_prefill", ms, T * d * (4 + 4 + 4 + 4 + 2))
+    wv = torch.ones(d, device=dev)
+    ms = timer(lambda: K.add_rmsnorm(x, yv, wv, 1e-5, hb))
+    note("add_rmsnorm_prefill", ms, T * d * (4 + 4 + 4 + 2))
+    ctx, table, pages = batch_ctx([T], [0])
+    C = 2 * H * D + 2 * G * D + G * V
+    proj, cw = rnd(T, C, dtype=torch.float32), rnd(C, 4, dtype=torch.float32)
+    st = torch.zeros(1, 3, C, device=dev)
+    kd, vd = torch.empty(pages, G, 16, 2 * D, dtype=bf, device=dev), torch.empty(pages, G, 16, V, dtype=bf, device=dev)
+    qn, inv = torch.ones(D, device=dev), torch.rand(D // 2, device=dev)
+    qo = torch.empty(T, 2 * H * D, dtype=bf, device=dev)
+    ms = timer(lambda: L.qkv_prepare(proj, cw, 4, st, qn, qn, 1e-5, inv, ctx.positions, ctx.tok_entry, ctx.entry_q_start,
+                                     ctx.entry_slot, table, qo, kd, vd, 16, 2 * H, 2 * G, G, D, V))
+    note("qkv_prepare_prefill", ms, T * C * (4 + 2))
+    Dq = 2 * D
+    qkv = rnd(T, (H + 2 * G) * Dq)
+    k2, v2 = torch.empty(pages, G, 16, Dq, dtype=bf, device=dev), torch.empty(pages, G, 16, Dq, dtype=bf, device=dev)
+    inv2 = torch.rand(Dq // 2, device=dev)
+    ms = timer(lambda: K.rope_cache(qkv, ctx.positions, ctx.tok_entry, table, inv2, k2, v2, H, G, Dq, 16))
+    note("rope_cache_prefill", ms, T * (H + 2 * G) * Dq * 2 * 2)
+    return rows
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="design_bench")
+    ap.add_argument("--sizes", default="s,m")
+    ap.add_argument("--prompt", type=int, default=2048)
+    ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--kernels-at", default="m", help="the size whose kernels are timed alone ('' for none)")
+    args = ap.parse_args(argv)
+    import torch
+    from infero_b200 import kernels as K
+    K.lib()
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
+            m = json.load(f)
+        peaks = {"hbm_gbs": float(m["hbm_gbs"]), "bf16_tflops": float(m["bf16_tflops"]), "source": "measured"}
+    except (OSError, KeyError, ValueError):
+        pass
+    timer = _Timer()
+    out = {"bench": "designs", "dtype": "bf16", "data": "synthetic", "prompt": args.prompt, "context": args.context,
+           "batch": args.batch, "layers": args.layers, "peaks": peaks, "sizes": {}}
+    for name in [s for s in args.sizes.split(",") if s]:
+        z = SIZES[name]
+        out["sizes"][name] = {"shape": z,
+                              "vufizen": time_model(vufizen_config(z, args.layers), args.prompt, args.context, args.batch, timer),
+                              "qwen2": time_model(qwen2_config(z, args.layers), args.prompt, args.context, args.batch, timer)}
+        print(f"[design_bench] {name}: {json.dumps(out['sizes'][name])}", file=sys.stderr, flush=True)
+    if args.kernels_at:
+        out["kernels"] = {"size": args.kernels_at,
+                          "rows": time_kernels(SIZES[args.kernels_at], args.prompt, args.context, args.batch, timer, peaks)}
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,361 @@
+"""The Vufizen decoder in the engine against the plain statement (tests/plain_vufizen.py): each mechanism's
+kernels alone, then whole models through the step function, the cache manager and the scheduler."""
+import math
+import types
+
+import numpy as np
+import pytest
+import torch
+
+import plain_vufizen as PV
+import replay_util as R
+from engine_fixtures import make_runner
+from vufizen_fixtures import CONFIGS, TOL, make_requests, model_dir, plain_logits, plain_model
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _rel(got, ref):
+    ref = ref.double()
+    return float((got.double().cpu() - ref).abs().max() / ref.abs().max())
+
+
+# ---- mechanisms alone --------------------------------------------------------------------------------------
+def test_gated_norm_add_kernel():
+    from infero_b200.kernels import layer_ops as L
+    g = torch.Generator().manual_seed(0)
+    T, d = 7, 52
+    x, y = torch.randn(T, d, generator=g) * 3, torch.randn(T, d, generator=g)
+    G, b, w = torch.randn(d, d, generator=g) * 0.2, torch.randn(d, generator=g), torch.tensor([1.3])
+    want = PV.gated_update(x.double(), y.double(), G.double(), b.double(), 1.3, 1e-5)
+    xd, logits = x.to(DEV), (x @ G.T).to(DEV)
+    h = torch.empty(T, d, dtype=torch.bfloat16, device=DEV)
+    L.gated_scalar_norm_add(xd, y.to(DEV), logits, b.to(DEV), w.to(DEV), 1e-5, h)
+    assert _rel(xd, want) < 2e-6
+    assert torch.equal(h, xd.to(torch.bfloat16))
+    # without a gate
+    xd = x.to(DEV)
+    L.gated_scalar_norm_add(xd, y.to(DEV), None, None, w.to(DEV), 1e-5, None)
+    assert _rel(xd, x.double() + 1.3 * PV.unit_rms(y.double(), 1e-5)) < 2e-6
+
+
+@pytest.mark.parametrize("H,D,V", [(2, 16, 32), (1, 12, 20), (3, 48, 64), (2, 128, 128), (1, 200, 40)])
+def test_hgrn2_scan_kernel(H, D, V):
+    """Three requests of unequal length in one launch, then continued from their state slots in a second one
+    in another order; slots are not the entries' indices."""
+    from infero_b200.kernels import layer_ops as L
+    g = torch.Generator().manual_seed(H * 100 + D)
+    d = 24
+    lens, slots = [9, 1, 20], [4, 0, 2]
+    wq, wf, wv = (torch.randn(n, d, generator=g) * 0.4 for n in (H * D, H * D, H * V))
+    bf, lower, wn = torch.randn(H * D, generator=g), torch.rand(H * D, generator=g), 1 + 0.1 * torch.randn(V, generator=g)
+    hs = [torch.randn(2 * n + 3, d, generator=g) for n in lens]
+    state = torch.randn(6, H, D, V, device=DEV)                       # stale numbers of requests that ended
+    for s in slots:
+        state[s].zero_()
+    stack = torch.cat([wq, wf, wv]).to(DEV)
+    got = [[] for _ in lens]
+    for part, order in ((0, [0, 1, 2]), (1, [2, 0, 1])):
+        rows = [hs[i][:lens[i]] if part == 0 else hs[i][lens[i]:] for i in order]
+        proj = (torch.cat(rows).to(DEV) @ stack.T).contiguous()
+        ql = [r.shape[0] for r in rows]
+        qs = np.concatenate([[0], np.cumsum(ql)[:-1]])
+        i32 = lambda a: torch.tensor(list(a), dtype=torch.int32, device=DEV)      # noqa: E731
+        out = torch.empty(proj.shape[0], H * V, device=DEV)
+        L.hgrn2_scan(proj, 0, H * D, 2 * H * D, bf.to(DEV), lower.to(DEV), wn.to(DEV), 1e-5, state, i32(qs), i32(ql),
+                     i32(slots[i] for i in order), out, len(order), H, D, V)
+        for k, i in enumerate(order):
+            got[i].append(out[qs[k]:qs[k] + ql[k]].cpu())
+    eye = torch.eye(H * V, dtype=torch.float64)
+    for i in range(len(lens)):
+        want, S = PV.hgrn2(hs[i].double(), wq.double(), wf.double(), bf.double(), lower.double(), wv.double(), wn.double(),
+                           eye, H, D, V, 1e-5)
+        assert _rel(torch.cat(got[i]), want) < 2e-5
+        assert _rel(state[slots[i]], S) < 2e-5
+
+
+@pytest.mark.parametrize("dtype,E,top,d,ff,T", [("float32", 6, 2, 40, 12, 9), ("float32", 3, 3, 20, 7, 3), ("bfloat16", 8, 3, 64, 24, 150),
+                                               ("bfloat16", 5, 1, 72, 40, 70), ("bfloat16", 4, 2, 64, 16, 2)])
+def test_routing_and_experts(dtype, E, top, d, ff, T):
+    """Router, choice, weights and the experts (streamed for few tokens and on the 32-bit path, grouped tensor-core
+    products for many tokens in bf16) against the plain statement on the same rounded numbers."""
+    from infero_b200.kernels import layer_ops as L, moe as M
+    td = torch.float32 if dtype == "float32" else torch.bfloat16
+    g = torch.Generator().manual_seed(E * 10 + top)
+    rt = lambda *s, k=1.0: (torch.randn(*s, generator=g) * k).to(td)             # noqa: E731
+    h, router, sg = rt(T, d), rt(E, d, k=0.5), rt(d, k=0.3)
+    gate, up, down = rt(E, ff, d, k=0.3), rt(E, ff, d, k=0.3), rt(E, d, ff, k=0.3)
+    shared = torch.randn(T, d, generator=g)
+    idx, w, sgate = L.moe_route(h.to(DEV), router.to(DEV), sg.to(DEV), top)
+    want_idx, want_w = PV.route(h.double(), router.double(), top)
+    assert torch.equal(idx.cpu().long(), want_idx)
+    assert _rel(w, want_w) < 1e-5 and _rel(sgate, torch.sigmoid(h.double() @ sg.double())) < 1e-5
+    gu = torch.stack([gate, up], dim=2).reshape(E, 2 * ff, d).contiguous().to(DEV)
+    y = torch.empty(T, d, device=DEV)
+    M.experts(h.to(DEV), gu, down.to(DEV), idx, w, shared.to(DEV), sgate, y)
+    pw = {"router": router.double(), "shared.sg": sg.double().unsqueeze(0)}
+    for e in range(E):
+        pw.update({f"e{e}.gate": gate[e].double(), f"e{e}.up": up[e].double(), f"e{e}.down": down[e].double()})
+    want = PV.moe(h.double(), pw, {"router": {"top": top}}) + torch.sigmoid(h.double() @ sg.double()).unsqueeze(1) * shared.double()
+    assert _rel(y, want) < (2e-5 if dtype == "float32" else 2e-2)
+
+
+def test_the_lowest_index_wins_a_tie_between_experts():
+    from infero_b200.kernels import layer_ops as L
+    h = torch.ones(2, 8, device=DEV)
+    router = torch.zeros(5, 8, device=DEV)
+    router[1] = router[3] = 0.25
+    idx, w, _ = L.moe_route(h, router, None, 3)
+    assert idx.cpu().tolist() == [[1, 3, 0], [1, 3, 0]]
+    e = math.exp(-2.0)
+    assert torch.allclose(w.cpu(), torch.tensor([[1 / (2 + e), 1 / (2 + e), e / (2 + e)]] * 2), atol=1e-6)
+
+
+class _Attn:
+    """One differential-attention layer over a hand-made paged cache: requests get shuffled pages, portions
+    are fed in steps, the kernels of the mixer are called as the mixer calls them."""
+
+    def __init__(self, dtype, H, G, D, V, taps, rot, page=16, pages=64, seed=0):
+        self.td = torch.float32 if dtype == "float32" else torch.bfloat16
+        self.H, self.G, self.D, self.V, self.taps, self.rot, self.page = H, G, D, V, taps, rot, page
+        g = torch.Generator().manual_seed(seed)
+        self.C = 2 * H * D + 2 * G * D + G * V
+        self.conv = (torch.randn(self.C, taps, generator=g) * 0.5) if taps else None
+        self.qn, self.kn = 1 + 0.2 * torch.randn(D, generator=g), 1 + 0.2 * torch.randn(D, generator=g)
+        self.base = 500.0
+        self.inv = torch.tensor([self.base ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float32) if rot else None
+        self.k = torch.full((pages, G, page, 2 * D), float("nan"), dtype=self.td, device=DEV)
+        self.v = torch.full((pages, G, page, V), float("nan"), dtype=self.td, device=DEV)
+        self.free = [int(p) for p in torch.randperm(pages, generator=g)]
+        self.table = {}
+        self.length = {}
+        self.state = torch.randn(8, max(taps - 1, 1), self.C, device=DEV)
+        self.lam, self.diff, self.scale, self.eps = 0.45, 0.3, 0.35, 1e-5
+
+    def step(self, parts):
+        """parts: [(request, slot, proj rows [n, C] float32)] -> attention output rows per request."""
+        from infero_b200.kernels import diff_attention as A, layer_ops as L
+        ql, pos0, slots, rows = [], [], [], []
+        for rid, slot, proj in parts:
+            if rid not in self.table:
+                self.table[rid], self.length[rid] = [], 0
+                self.state[slot].zero_()
+            n = proj.shape[0]
+            while len(self.table[rid]) * self.page < self.length[rid] + n:
+                self.table[rid].append(self.free.pop())
+            ql.append(n), pos0.append(self.length[rid]), slots.append(slot), rows.append(proj)
+        E, width = len(parts), 40
+        table = torch.full((E, width), -1, dtype=torch.int32)
+        for e, (rid, _, _) in enumerate(parts):
+            table[e, :len(self.table[rid])] = torch.tensor(self.table[rid], dtype=torch.int32)
+        qs = np.concatenate([[0], np.cumsum(ql)[:-1]]).astype(np.int32)
+        i32 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=DEV)       # noqa: E731
+        ctx = types.SimpleNamespace(n_entries=E, h_q_len=np.asarray(ql, dtype=np.int32), h_pos0=np.asarray(pos0, dtype=np.int32),
+                                    tok_entry=i32(np.repeat(np.arange(E), ql)),
+                                    positions=i32(np.concatenate([p + np.arange(n) for p, n in zip(pos0, ql)])),
+                                    entry_q_start=i32(qs), entry_q_len=i32(ql), entry_pos0=i32(pos0), entry_slot=i32(slots))
+        proj = torch.cat(rows).to(DEV).contiguous()
+        T = proj.shape[0]
+        H, G, D, V = self.H, self.G, self.D, self.V
+        q = torch.empty(T, 2 * H * D, dtype=self.td, device=DEV)
+        dev = lambda t: None if t is None else t.to(DEV)                          # noqa: E731
+        table = table.to(DEV)
+        L.qkv_prepare(proj, dev(self.conv), self.taps, self.state if self.taps > 1 else None, dev(self.qn), dev(self.kn),
+                      self.eps, dev(self.inv), ctx.positions, ctx.tok_entry, ctx.entry_q_start, ctx.entry_slot, table, q,
+                      self.k, self.v, self.page, 2 * H, 2 * G, G, D, V)
+        if self.taps > 1:
+            L.conv_state_update(proj, self.state, self.taps, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_slot, E, self.C)
+        out = torch.empty(T, H * V, dtype=self.td, device=DEV)
+        kv = types.SimpleNamespace(k=self.k, v=self.v, page_size=self.page)
+        A.paged_diff_attention(ctx, q, out, kv, table, H, G, D, V, None, self.scale, self.lam, self.eps, 1 - self.diff)
+        res = {}
+        for e, (rid, _, _) in enumerate(parts):
+            res[rid] = out[qs[e]:qs[e] + ql[e]].float().cpu()
+            self.length[rid] += ql[e]
+        return res
+
+    def close(self, rid):
+        self.free = self.table.pop(rid) + self.free          # given back pages are handed out again first
+        del self.length[rid]
+
+    def plain(self, proj):
+        """The same layer on a whole sequence of product rows."""
+        H, G, D, V = self.H, self.G, self.D, self.V
+        T = proj.shape[0]
+        u = proj.double()
+        if self.taps:
+            u = PV.causal_conv(u, self.conv.double())
+        q, k, v = u[:, :2 * H * D], u[:, 2 * H * D:2 * (H + G) * D], u[:, 2 * (H + G) * D:]
+        q = PV.unit_rms(q.reshape(T, 2 * H, D), self.eps) * self.qn.double()
+        k = PV.unit_rms(k.reshape(T, 2 * G, D), self.eps) * self.kn.double()
+        if self.rot:
+            q, k = (PV.rotate_adjacent(t, torch.arange(T), self.base, self.rot) for t in (q, k))
+        q, k, v = q.view(T, H, 2, D), k.view(T, G, 2, D), v.reshape(T, G, V)
+        heads = []
+        for h in range(H):
+            g = h // (H // G)
+            a = [PV.softmax_causal(q[:, h, m] @ k[:, g, m].T * self.scale) @ v[:, g] for m in range(2)]
+            heads.append(PV.differential_combine(a[0], a[1], self.lam, self.diff, self.eps))
+        return torch.cat(heads, dim=-1)
+
+
+ATTN_CASES = [("float32", 2, 1, 12, 20, 4, 6), ("float32", 3, 3, 10, 14, 0, 10), ("bfloat16", 4, 2, 32, 48, 3, 16),
+              ("bfloat16", 2, 1, 64, 128, 4, 64), ("bfloat16", 2, 2, 24, 40, 2, 0)]
+
+
+@pytest.mark.parametrize("dtype,H,G,D,V,taps,rot", ATTN_CASES)
+def test_differential_attention_in_portions_and_single_tokens(dtype, H, G, D, V, taps, rot):
+    """Two requests: portions of many sizes (down to one token, cut inside the convolution's reach and inside
+    pages), decoding beside a prompt, a slot and pages used again by a third request."""
+    a = _Attn(dtype, H, G, D, V, taps, rot, seed=D)
+    g = torch.Generator().manual_seed(1)
+    n = {"x": 150, "y": 61, "z": 70}
+    proj = {r: torch.randn(k, a.C, generator=g) * 1.5 for r, k in n.items()}
+    got = {r: [] for r in n}
+    at = {r: 0 for r in n}
+
+    def run(*parts):
+        res = a.step([(r, s, proj[r][at[r]:at[r] + k]) for r, s, k in parts])
+        for r, _, k in parts:
+            got[r].append(res[r])
+            at[r] += k
+    run(("x", 3, 70), ("y", 1, 2))
+    run(("y", 1, 1), ("x", 3, 1))
+    run(("y", 1, 1), ("x", 3, 2))                       # a single token in front, a portion of two behind it
+    run(("x", 3, 30), ("y", 1, 17))
+    for _ in range(20):
+        run(("x", 3, 1), ("y", 1, 1))                   # decoding across a page border (y: 21 .. 41)
+    run(("y", 1, 20))
+    a.close("y")
+    run(("z", 1, 33), ("x", 3, 1))                      # z on y's slot and pages
+    run(("x", 3, 26), ("z", 1, 37))
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    for r in n:
+        assert at[r] == n[r]
+        assert _rel(torch.cat(got[r]), a.plain(proj[r])) < tol, r
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("far", [0, 1, 15, 16, 17, 255, 256, 300, 310])
+def test_a_far_key_is_found(dtype, far):
+    """One key among hundreds matches the last queries in map 1 (its score stands out by scaling that key and those
+    queries); its value then dominates a1.  Keys at the sequence's start, on both sides of page borders and far
+    back, read from a prompt portion and from single tokens."""
+    H, G, D, V = 2, 1, 32, 64
+    a = _Attn(dtype, H, G, D, V, 0, 0, seed=3)
+    a.qn, a.kn = torch.ones(D), torch.ones(D)
+    g = torch.Generator().manual_seed(far)
+    n = 330
+    proj = torch.randn(n, a.C, generator=g) * 0.3
+    u = torch.randn(D, generator=g)
+    proj[far, 2 * H * D:2 * H * D + D] = 3 * u                    # map 1 of the key at `far`
+    for p in range(n - 12, n):
+        proj[p, :D] = 3 * u                                        # map 1 of head 0 of the last queries
+    proj[far, 2 * (H + G) * D:] += 2.0                             # and a value that shows
+    want = a.plain(proj)
+    first = a.step([("r", 0, proj[:n - 8])])["r"]
+    rest = [a.step([("r", 0, proj[p:p + 1])])["r"] for p in range(n - 8, n)]
+    got = torch.cat([first] + rest)
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    assert _rel(got, want) < tol
+    # the crafted key carries the result: without it the last rows differ by far more than the tolerance
+    proj2 = proj.clone()
+    proj2[far, 2 * H * D:2 * H * D + D] = 0
+    if far < n - 12:
+        assert _rel(a.plain(proj2)[-8:], want[-8:]) > 10 * tol
+
+
+# ---- whole models through the step function ---------------------------------------------------------------------
+def _replay(name, dtype, steps_of, lengths, seed=0, page_size=16, max_seqs=3, tol=None):
+    mdir = model_dir(name)
+    reqs = make_requests(name, lengths, seed=seed)
+    plain = plain_logits(mdir, reqs)
+    steps = steps_of(reqs)
+    runner = make_runner(mdir, dtype, R.max_live_tokens(steps, reqs), page_size=page_size, max_seqs=max_seqs)
+    got = R.replay_inprocess(runner, steps)
+    assert len(got) > 0
+    worst, where = R.compare(got, plain)
+    assert worst <= (tol or TOL[dtype]), f"{name} {dtype}: {worst:.3e} at {where}"
+    assert not runner.manager.requests
+    return runner
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("D", "bfloat16"), ("B", "float32"), ("C", "float32"), ("C", "bfloat16")])
+def test_whole_prompts(name, dtype):
+    _replay(name, dtype, R.steps_whole, [1, 2, 15, 16, 17, 33, 131], tol=0.03 if (name, dtype) == ("C", "bfloat16") else None)
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("D", "bfloat16"), ("B", "float32"), ("C", "float32")])
+def test_prompt_then_token_by_token(name, dtype):
+    _replay(name, dtype, lambda r: R.steps_tail_decode(r, tail=40), [90, 41, 5])
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("D", "bfloat16"), ("B", "float32"), ("C", "bfloat16")])
+def test_portions_down_to_two_tokens(name, dtype):
+    _replay(name, dtype, lambda r: R.steps_chunked(r, seed=2), [150, 64, 31])
+    _replay(name, dtype, lambda r: R.steps_chunked(r, seed=5, sizes=(1, 2, 1, 3, 2, 16, 1, 15, 17)), [70])
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("D", "bfloat16"), ("B", "float32"), ("C", "float32")])
+def test_mixed_batches_with_slots_and_pages_used_again(name, dtype):
+    """Three live requests in exactly three state slots: every later request starts in a slot and on pages that
+    an ended one gave back."""
+    runner = _replay(name, dtype, lambda r: R.steps_mixed(r, seed=4, max_live=3), [120, 33, 80, 17, 64, 95, 2], max_seqs=3)
+    if runner.manager.groups:
+        assert runner.manager.pages_reused > 0
+
+
+def test_a_batch_equals_each_request_alone_bitwise_in_32_bit():
+    """On the 32-bit path what is computed for a token does not depend on what else is in the step."""
+    mdir = model_dir("A")
+    reqs = make_requests("A", [50, 21, 37], seed=9)
+    together = R.replay_inprocess(make_runner(mdir, "float32", 256, max_seqs=3), [
+        {"step": 0, "entries": [{"id": r, "tokens": t, "want": list(range(len(t)))} for r, t in reqs.items()], "end": list(reqs)}])
+    alone = R.replay_inprocess(make_runner(mdir, "float32", 256, max_seqs=3), R.steps_whole(reqs))
+    assert together.keys() == alone.keys()
+    for k in alone:
+        assert np.array_equal(together[k], alone[k]), k
+
+
+def test_three_hundred_single_tokens():
+    _replay("B", "float32", lambda r: R.steps_tail_decode(r, tail=300), [310])
+    _replay("D", "bfloat16", lambda r: R.steps_tail_decode(r, tail=300), [305])
+
+
+def test_page_size_64():
+    _replay("D", "bfloat16", lambda r: R.steps_mixed(r, seed=1, max_live=2), [130, 70, 64], page_size=64)
+
+
+# ---- the engine's own entry point --------------------------------------------------------------------------------
+def _plain_greedy(cfg, w, prompt, n):
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(PV.forward(cfg, w, toks)[-1].argmax()))
+    return toks[len(prompt):]
+
+
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_greedy_generation_through_the_scheduler(name):
+    """Several prompts queued at once, more than there are request slots, prompts cut into portions by the
+    scheduler's budget, decode steps replayed from captured graphs."""
+    from infero_b200.engine import Engine
+    from infero_b200.sampling import SamplingParams
+    mdir = model_dir(name)
+    cfg, w = plain_model(mdir)
+    prompts = list(make_requests(name, [19, 40, 3, 27], seed=21).values())
+    eng = Engine(mdir, dtype="float32", ctx=128, max_seqs=2, kv_slots=2 * 128, max_batch_tokens=32, cuda_graphs=True)
+    params = SamplingParams(temperature=0.0, repetition_penalty=1.0)
+    got = eng.generate(prompts, params, max_new_tokens=10, ignore_eos=True)
+    for p, g in zip(prompts, got):
+        assert g == _plain_greedy(cfg, w, p, 10)
+    assert eng.runner.graph_replays > 0
+
+
+def test_the_trace_runner_replays_a_vufizen_folder(tmp_path):
+    mdir = model_dir("A")
+    reqs = make_requests("A", [70, 30], seed=2)
+    steps = R.steps_mixed(reqs, seed=3, max_live=2)
+    got = R.replay_subprocess(mdir, "float32", steps, R.max_live_tokens(steps, reqs), str(tmp_path), CONFIGS["A"]["vocab"])
+    worst, where = R.compare(got, plain_logits(mdir, reqs))
+    assert worst <= TOL["float32"], (worst, where)
