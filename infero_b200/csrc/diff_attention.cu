@@ -31,8 +31,8 @@ qkv_prepare_kernel(const float* __restrict__ proj, int stride, const float* __re
                    const int* __restrict__ entry_q_start, const int* __restrict__ entry_slot,
                    const int* __restrict__ block_table, int max_blocks, T* __restrict__ q_out, int q_stride,
                    T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int n_q_units, int n_k_units,
-                   int G, int D, int V, int write_cache) {
-    extern __shared__ float buf[];            // this token's channels after the convolution
+                   int G, int D, int V, int write_cache, int q_pad) {
+    extern __shared__ float buf[];            // this token's channels after the convolution, then rot/2 (cos, sin)
     const int t = blockIdx.x;
     const int e = tok_entry[t];
     const int r = t - entry_q_start[e];       // index of the token among its request's new tokens
@@ -55,6 +55,12 @@ qkv_prepare_kernel(const float* __restrict__ proj, int stride, const float* __re
         }
         buf[c] = acc;
     }
+    float2* cs_tab = reinterpret_cast<float2*>(buf + ((C + 1) & ~1));
+    for (int i = threadIdx.x; i < rot / 2; i += PREP_THREADS) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);          // once per token, shared by all heads and maps
+        cs_tab[i] = make_float2(cs, sn);
+    }
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = PREP_THREADS / 32;
     for (int u = warp; u < n_q_units + n_k_units; u += nwarps) {
@@ -69,15 +75,25 @@ qkv_prepare_kernel(const float* __restrict__ proj, int stride, const float* __re
             __syncwarp();
         }
         for (int i = lane; i < rot / 2; i += 32) {
-            float sn, cs;
-            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            const float cs = cs_tab[i].x, sn = cs_tab[i].y;
             const float a = x[2 * i], b = x[2 * i + 1];
             x[2 * i] = a * cs - b * sn;
             x[2 * i + 1] = b * cs + a * sn;
         }
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < Cq; c += PREP_THREADS) q_out[(size_t)t * q_stride + c] = from_f32<T>(buf[c]);
+    if (q_pad) {
+        // every map as a query of its own, as wide as a whole key row, with zeros where the other map's columns are:
+        // unit u = 2 head + map goes to columns [2 D u + D map, + D)
+        for (int c = threadIdx.x; c < Cq; c += PREP_THREADS) {
+            const int u = c / D, i = c - u * D, m = u & 1;
+            T* dst = q_out + (size_t)t * q_stride + (size_t)u * 2 * D;
+            dst[m * D + i] = from_f32<T>(buf[c]);
+            dst[(1 - m) * D + i] = from_f32<T>(0.f);
+        }
+    } else {
+        for (int c = threadIdx.x; c < Cq; c += PREP_THREADS) q_out[(size_t)t * q_stride + c] = from_f32<T>(buf[c]);
+    }
     if (!write_cache) return;
     const int page = block_table[(size_t)e * max_blocks + pos / page_size];
     if (page < 0) return;
@@ -203,9 +219,54 @@ diff_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restri
     }
 }
 
+// maps [tokens, H, 2, V] (each map's attention result) -> out [tokens, H, V]: a1 - lambda a2, divided by its root
+// mean square over V (plus eps), times out_scale.  One warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32)
+diff_combine_kernel(const T* __restrict__ maps, int maps_stride, T* __restrict__ out, int out_stride, int n_tokens, int H,
+                    int V, float lambda, float eps, float out_scale) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * WARPS + warp;
+    if (item >= (long long)n_tokens * H) return;
+    const int t = (int)(item / H), h = (int)(item % H);
+    const T* a1 = maps + (size_t)t * maps_stride + (size_t)h * 2 * V;
+    const T* a2 = a1 + V;
+    float o[MAX_V / 32];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_V / 32; ++i) {
+        const int dd = i * 32 + lane;
+        o[i] = dd < V ? to_f32(a1[dd]) - lambda * to_f32(a2[dd]) : 0.f;
+        ss = fmaf(o[i], o[i], ss);
+    }
+    ss = warp_sum(ss);
+    const float r = out_scale / sqrtf(ss / (float)V + eps);
+    T* orow = out + (size_t)t * out_stride + (size_t)h * V;
+#pragma unroll
+    for (int i = 0; i < MAX_V / 32; ++i) {
+        const int dd = i * 32 + lane;
+        if (dd < V) orow[dd] = from_f32<T>(o[i] * r);
+    }
+}
+
 }  // namespace
 
 extern "C" {
+
+int infero_diff_combine(const void* maps, int maps_stride, void* out, int out_stride, int dtype, int n_tokens, int H, int V,
+                        float lambda, float eps, float out_scale, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    INFERO_REQUIRE(V >= 1 && V <= MAX_V, "diff combine: value width %d outside 1..%d", V, MAX_V);
+    const unsigned blocks = (unsigned)(((long long)n_tokens * H + WARPS - 1) / WARPS);
+    if (dtype == INFERO_F32)
+        diff_combine_kernel<float><<<blocks, WARPS * 32, 0, stream>>>((const float*)maps, maps_stride, (float*)out, out_stride,
+                                                                      n_tokens, H, V, lambda, eps, out_scale);
+    else
+        diff_combine_kernel<bf16><<<blocks, WARPS * 32, 0, stream>>>((const bf16*)maps, maps_stride, (bf16*)out, out_stride,
+                                                                     n_tokens, H, V, lambda, eps, out_scale);
+    return infero_check_launch("diff_combine");
+}
+
 
 // proj float32 [tokens, stride]: columns [q (n_q_units*D) | k (n_k_units*D) | v (G*V)] in front.
 // conv_w float32 [C, taps] for those C channels in that order; conv_state float32 [slots, taps-1, C].
@@ -215,25 +276,25 @@ int infero_qkv_prepare(const float* proj, int stride, const float* conv_w, int t
                        const int* positions, const int* tok_entry, const int* entry_q_start, const int* entry_slot,
                        const int* block_table, int max_blocks, void* q_out, int q_stride, void* k_cache, void* v_cache,
                        int dtype, int page_size, int n_tokens, int n_q_units, int n_k_units, int G, int D, int V,
-                       int write_cache, cudaStream_t stream) {
+                       int write_cache, int q_pad, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     INFERO_REQUIRE(taps <= MAX_TAPS, "qkv_prepare: %d taps, at most %d", taps, MAX_TAPS);
     INFERO_REQUIRE(G > 0 && n_k_units % G == 0 && rot % 2 == 0 && rot <= D, "qkv_prepare: bad sizes");
     const int C = (n_q_units + n_k_units) * D + G * V;
-    const size_t smem = (size_t)C * sizeof(float);
+    const size_t smem = (size_t)(((C + 1) & ~1) + rot) * sizeof(float);
     INFERO_REQUIRE(smem <= 200 * 1024, "qkv_prepare: %d channels do not fit shared memory", C);
     if (dtype == INFERO_F32) {
         auto kern = qkv_prepare_kernel<float>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         kern<<<n_tokens, PREP_THREADS, smem, stream>>>(proj, stride, conv_w, taps, conv_state, q_norm, k_norm, eps,
             inv_freq, rot, positions, tok_entry, entry_q_start, entry_slot, block_table, max_blocks, (float*)q_out,
-            q_stride, (float*)k_cache, (float*)v_cache, page_size, n_q_units, n_k_units, G, D, V, write_cache);
+            q_stride, (float*)k_cache, (float*)v_cache, page_size, n_q_units, n_k_units, G, D, V, write_cache, q_pad);
     } else {
         auto kern = qkv_prepare_kernel<bf16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         kern<<<n_tokens, PREP_THREADS, smem, stream>>>(proj, stride, conv_w, taps, conv_state, q_norm, k_norm, eps,
             inv_freq, rot, positions, tok_entry, entry_q_start, entry_slot, block_table, max_blocks, (bf16*)q_out,
-            q_stride, (bf16*)k_cache, (bf16*)v_cache, page_size, n_q_units, n_k_units, G, D, V, write_cache);
+            q_stride, (bf16*)k_cache, (bf16*)v_cache, page_size, n_q_units, n_k_units, G, D, V, write_cache, q_pad);
     }
     return infero_check_launch("qkv_prepare");
 }

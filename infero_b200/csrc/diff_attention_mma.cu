@@ -160,10 +160,37 @@ int launch_prefill(const void* q, int q_stride, void* out, int out_stride, const
 }
 
 // ---- single tokens ------------------------------------------------------------------------------------------
-constexpr int DW = 8;              // warps of a block
+constexpr int DW = 16;             // warps of a block
 constexpr int MAX_D = 256, MAX_V = 256;
 
-template <typename T>
+// q . k over n elements; bf16 rows whose length is a multiple of 8 are read 16 bytes at a time
+__device__ __forceinline__ float dot_q(const float* __restrict__ q, const float* __restrict__ k, int n) {
+    float d = 0.f;
+    for (int i = 0; i < n; ++i) d = fmaf(q[i], k[i], d);
+    return d;
+}
+__device__ __forceinline__ float dot_q(const float* __restrict__ q, const bf16* __restrict__ k, int n) {
+    float d = 0.f;
+    if ((n & 7) == 0 && ((uintptr_t)k & 15) == 0) {
+        for (int i = 0; i < n; i += 8) {
+            const uint4 u = *reinterpret_cast<const uint4*>(k + i);
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(p[j]);
+                d = fmaf(q[i + 2 * j], f.x, d);
+                d = fmaf(q[i + 2 * j + 1], f.y, d);
+            }
+        }
+        return d;
+    }
+    for (int i = 0; i < n; ++i) d = fmaf(q[i], __bfloat162float(k[i]), d);
+    return d;
+}
+
+// PAIR: a lane owns adjacent value columns (2 lane, 2 lane + 1) of every block of 64 (bf16 pairs, 4-byte loads);
+// else column lane of every block of 32.
+template <typename T, bool PAIR>
 __global__ void __launch_bounds__(DW * 32)
 diff_attn_decode_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
                         const T* __restrict__ k_cache, const T* __restrict__ v_cache,
@@ -198,10 +225,7 @@ diff_attn_decode_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
             if (page >= 0) {
                 row = ((long long)page * G + g) * page_size + (j % page_size);
                 const T* kr = k_cache + row * 2 * D;
-                float d1 = 0.f, d2 = 0.f;
-                for (int i = 0; i < D; ++i) d1 = fmaf(q_s[i], to_f32(kr[i]), d1);
-                for (int i = 0; i < D; ++i) d2 = fmaf(q_s[D + i], to_f32(kr[D + i]), d2);
-                s1 = d1 * scale, s2 = d2 * scale;
+                s1 = dot_q(q_s, kr, D) * scale, s2 = dot_q(q_s + D, kr + D, D) * scale;
             }
         }
         const float n1 = fmaxf(m1, warp_max(s1)), n2 = fmaxf(m2, warp_max(s2));
@@ -217,22 +241,36 @@ diff_attn_decode_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
             const float pa = __shfl_sync(0xffffffffu, p1, jj), pb = __shfl_sync(0xffffffffu, p2, jj);
             if (rj < 0) continue;
             const T* vr = v_cache + rj * V;
+            if (PAIR) {
 #pragma unroll
-            for (int i = 0; i < MAX_V / 32; ++i) {
-                const int dd = i * 32 + lane;
-                if (dd < V) {
-                    const float v = to_f32(vr[dd]);
-                    acc1[i] = fmaf(pa, v, acc1[i]);
-                    acc2[i] = fmaf(pb, v, acc2[i]);
+                for (int i = 0; i < MAX_V / 64; ++i) {
+                    const int dd = i * 64 + 2 * lane;
+                    if (dd < V) {
+                        const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>((const bf16*)vr + dd));
+                        acc1[2 * i] = fmaf(pa, v.x, acc1[2 * i]), acc1[2 * i + 1] = fmaf(pa, v.y, acc1[2 * i + 1]);
+                        acc2[2 * i] = fmaf(pb, v.x, acc2[2 * i]), acc2[2 * i + 1] = fmaf(pb, v.y, acc2[2 * i + 1]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < MAX_V / 32; ++i) {
+                    const int dd = i * 32 + lane;
+                    if (dd < V) {
+                        const float v = to_f32(vr[dd]);
+                        acc1[i] = fmaf(pa, v, acc1[i]);
+                        acc2[i] = fmaf(pb, v, acc2[i]);
+                    }
                 }
             }
         }
         m1 = n1, m2 = n2;
     }
+    // the column register i of this lane holds
+    auto col = [&](int i) { return PAIR ? (i >> 1) * 64 + 2 * lane + (i & 1) : i * 32 + lane; };
     if (lane == 0) st[warp * 4 + 0] = m1, st[warp * 4 + 1] = l1, st[warp * 4 + 2] = m2, st[warp * 4 + 3] = l2;
 #pragma unroll
     for (int i = 0; i < MAX_V / 32; ++i) {
-        const int dd = i * 32 + lane;
+        const int dd = col(i);
         if (dd < V) accs[(warp * 2 + 0) * V + dd] = acc1[i], accs[(warp * 2 + 1) * V + dd] = acc2[i];
     }
     __syncthreads();
@@ -249,7 +287,7 @@ diff_attn_decode_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
         L2 = fmaf(st[w * 4 + 3], f2, L2);
 #pragma unroll
         for (int i = 0; i < MAX_V / 32; ++i) {
-            const int dd = i * 32 + lane;
+            const int dd = col(i);
             if (dd < V) {
                 acc1[i] = fmaf(accs[(w * 2 + 0) * V + dd], f1, acc1[i]);
                 acc2[i] = fmaf(accs[(w * 2 + 1) * V + dd], f2, acc2[i]);
@@ -260,7 +298,7 @@ diff_attn_decode_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < MAX_V / 32; ++i) {
-        const int dd = i * 32 + lane;
+        const int dd = col(i);
         acc1[i] = dd < V ? acc1[i] * i1 - acc2[i] * i2 : 0.f;
         ss = fmaf(acc1[i], acc1[i], ss);
     }
@@ -269,7 +307,7 @@ diff_attn_decode_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
     T* orow = out + (size_t)t * out_stride + (size_t)h * V;
 #pragma unroll
     for (int i = 0; i < MAX_V / 32; ++i) {
-        const int dd = i * 32 + lane;
+        const int dd = col(i);
         if (dd < V) orow[dd] = from_f32<T>(acc1[i] * r);
     }
 }
@@ -319,11 +357,15 @@ int infero_diff_attn_decode(const void* q, int q_stride, void* out, int out_stri
     const size_t smem = (size_t)(2 * D + DW * 4 + DW * 2 * V) * sizeof(float);
     const dim3 grid(n_tok, H);
     if (dtype == INFERO_F32)
-        diff_attn_decode_kernel<float><<<grid, DW * 32, smem, stream>>>((const float*)q, q_stride, (float*)out, out_stride,
+        diff_attn_decode_kernel<float, false><<<grid, DW * 32, smem, stream>>>((const float*)q, q_stride, (float*)out, out_stride,
             (const float*)k_cache, (const float*)v_cache, block_table, max_blocks, tok_entry, positions, H, G, D, V,
             page_size, window, scale, lambda, eps, out_scale);
+    else if (V % 2 == 0)
+        diff_attn_decode_kernel<bf16, true><<<grid, DW * 32, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride,
+            (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_blocks, tok_entry, positions, H, G, D, V,
+            page_size, window, scale, lambda, eps, out_scale);
     else
-        diff_attn_decode_kernel<bf16><<<grid, DW * 32, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride,
+        diff_attn_decode_kernel<bf16, false><<<grid, DW * 32, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride,
             (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_blocks, tok_entry, positions, H, G, D, V,
             page_size, window, scale, lambda, eps, out_scale);
     return infero_check_launch("diff_attn_decode");

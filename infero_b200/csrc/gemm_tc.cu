@@ -499,7 +499,11 @@ template <int EPI, typename OutT>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                           OutT* __restrict__ out, const void* __restrict__ bias, int bias_dtype,
-                          int RA, int RB, int K, long long ldc, int BN, int* __restrict__ err_flag) {
+                          int RA, int RB, int K, long long ldc, int BN, int* __restrict__ err_flag,
+                          const int* __restrict__ tile_group) {
+    // tile_group (or null): a grouped product.  map_b then covers several stacked [RB, K] matrices and the
+    // 128-row tile m of the activations multiplies matrix tile_group[m] (a negative entry: a tile of padding
+    // rows, multiplied with matrix 0).  The table is written by a kernel in front, so it is read after the wait.
     constexpr int STAGES = PERS_STAGES;
     using Plan = SmemPlan<PERS_MAX_BN, STAGES>;             // where the barriers sit; stages are packed by BN
     const int stage_bytes = A_STAGE_BYTES + BN * TILE_K * 2;
@@ -567,14 +571,20 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             // weights of the first stages before the kernel in front has finished, activations after
             const int pre = (int)(total < STAGES ? total : STAGES);
             int pa0[STAGES], pkx[STAGES];
+            if (tile_group) pdl_wait();
+            auto b_row = [&]() {                       // first row of this tile's weights in map_b
+                if (!tile_group) return b0;
+                const int grp = tile_group[a0 / TILE_A];
+                return b0 + (grp > 0 ? grp : 0) * RB;
+            };
             for (int it = 0; it < pre; ++it) {
                 mbar_expect_tx(&full_bar[it], stage_bytes);
-                tma_load_2d(smem + it * stage_bytes + A_STAGE_BYTES, &map_b, kt * TILE_K, b0, &full_bar[it]);
+                tma_load_2d(smem + it * stage_bytes + A_STAGE_BYTES, &map_b, kt * TILE_K, b_row(), &full_bar[it]);
                 pa0[it] = a0;
                 pkx[it] = kt * TILE_K;
                 advance();
             }
-            pdl_wait();
+            if (!tile_group) pdl_wait();
             for (int it = 0; it < pre; ++it) {
                 tma_load_2d(smem + it * stage_bytes, &map_a, pkx[it], pa0[it], &full_bar[it]);
                 issued = it + 1;
@@ -586,7 +596,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 uint8_t* sa = smem + s * stage_bytes;
                 mbar_expect_tx(&full_bar[s], stage_bytes);
                 tma_load_2d(sa, &map_a, kt * TILE_K, a0, &full_bar[s]);
-                tma_load_2d(sa + A_STAGE_BYTES, &map_b, kt * TILE_K, b0, &full_bar[s]);
+                tma_load_2d(sa + A_STAGE_BYTES, &map_b, kt * TILE_K, b_row(), &full_bar[s]);
                 issued = it + 1;
                 advance();
                 if (++s == STAGES) { s = 0; ph ^= 1u; }
@@ -969,7 +979,8 @@ int pick_tile_n(int M, int N, int ctas, int multiple) {
 
 template <int EPI, typename OutT>
 int launch_persistent(const void* x, const void* w, void* out, const void* bias, int bias_dtype,
-                      int RA, int RB, int K, int ldx, long long ldc, int sm_count, int* err, cudaStream_t stream) {
+                      int RA, int RB, int K, int ldx, long long ldc, int sm_count, int* err, cudaStream_t stream,
+                      const int* tile_group = nullptr, int n_groups = 1) {
     using Plan = SmemPlan<PERS_MAX_BN, PERS_STAGES>;
     auto kern = gemm_tc_persistent_kernel<EPI, OutT>;
     static bool configured = false;
@@ -985,11 +996,11 @@ int launch_persistent(const void* x, const void* w, void* out, const void* bias,
     const int bn = pick_tile_n(RA, RB, sms, EPI == EPI_ROW_SWIGLU ? 32 : 16);
     CUtensorMap ma, mb;
     if (get_map(x, RA, K, ldx, TILE_A, &ma)) return 1;
-    if (get_map(w, RB, K, K, bn, &mb)) return 1;
+    if (get_map(w, RB * n_groups, K, K, bn, &mb)) return 1;
     const int n_tiles = ((RA + TILE_A - 1) / TILE_A) * ((RB + bn - 1) / bn);
     const int ctas = n_tiles < sms ? n_tiles : sms;
     launch_pdl(kern, dim3(ctas), dim3(GEMM_THREADS), Plan::TOTAL, stream, ma, mb, (OutT*)out, bias, bias_dtype, RA, RB,
-               K, ldc, bn, err);
+               K, ldc, bn, err, tile_group);
     return infero_check_launch("gemm_tc_persistent");
 }
 
@@ -1352,6 +1363,26 @@ int infero_gemm_tc_swiglu(const void* x, const void* w, void* out, int M, int N,
         if (r >= 0) return r;
     }
     return launch_persistent<EPI_ROW_SWIGLU, bf16>(x, w, out, nullptr, 0, M, N, K, ldx, ldc, sm_count, err, stream);
+}
+
+// A grouped product on the persistent kernel: x [M, K] in tiles of 128 rows, w n_groups stacked [N, K] matrices,
+// tile m of x multiplies matrix tile_group[m] (device int32 [ceil(M / 128)]).  swiglu: w's rows alternate gate and
+// up and out is bf16 [M, N / 2]; else out is float32 [M, N].
+int infero_gemm_tc_grouped(const void* x, const void* w, void* out, int swiglu, int M, int N, int K, int ldx, int ldc,
+                           const int* tile_group, int n_groups, int sm_count, cudaStream_t stream) {
+    if (M == 0 || N == 0) return 0;
+    INFERO_REQUIRE(infero_gemm_tc_supported(x, w, M, N, K, ldx), "gemm_tc_grouped: shape M=%d N=%d K=%d ldx=%d not supported", M, N, K, ldx);
+    INFERO_REQUIRE(tile_group && n_groups >= 1 && (long long)N * n_groups < (1ll << 31), "gemm_tc_grouped: bad groups");
+    int* err;
+    if (err_flag_ptr(&err)) return 1;
+    if (swiglu) {
+        INFERO_REQUIRE(N % 2 == 0 && ldc >= N / 2, "gemm_tc_grouped: N=%d must be even and ldc=%d at least N/2", N, ldc);
+        return launch_persistent<EPI_ROW_SWIGLU, bf16>(x, w, out, nullptr, 0, M, N, K, ldx, ldc, sm_count, err, stream,
+                                                       tile_group, n_groups);
+    }
+    INFERO_REQUIRE(ldc >= N, "gemm_tc_grouped: ldc=%d below N=%d", ldc, N);
+    return launch_persistent<EPI_ROW, float>(x, w, out, nullptr, 0, M, N, K, ldx, ldc, sm_count, err, stream, tile_group,
+                                             n_groups);
 }
 
 // The few-token, one-split case of infero_gemm_tc_swiglu on an input that still lacks its norm's scalar:

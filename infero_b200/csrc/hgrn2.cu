@@ -60,12 +60,10 @@ hgrn2_scan_kernel(const float* __restrict__ proj, int stride, int q_off, int f_o
     const int i0 = s * DPT;
     float S[DPT];
     float* st = mode == WHOLE ? state + (((size_t)slot * H + h) * D) * V : st_chunk;
-    float P[DPT];                                            // product of the forget gates (LOCAL, threads of column 0)
 #pragma unroll
-    for (int ii = 0; ii < DPT; ++ii) {
-        S[ii] = (mode != LOCAL && active && i0 + ii < D) ? st[(size_t)(i0 + ii) * V + j] : 0.f;
-        P[ii] = 1.f;
-    }
+    for (int ii = 0; ii < DPT; ++ii) S[ii] = (mode != LOCAL && active && i0 + ii < D) ? st[(size_t)(i0 + ii) * V + j] : 0.f;
+    float* pd = part + TT * DS * V;                          // [D]: product of the forget gates (LOCAL)
+    for (int i = tid; i < D; i += nthreads) pd[i] = 1.f;
     const int lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
     for (int t0 = 0; t0 < n; t0 += TT) {
         const int nt = min(TT, n - t0);
@@ -94,10 +92,17 @@ hgrn2_scan_kernel(const float* __restrict__ proj, int stride, int q_off, int f_o
                         const float f = fs[tt * D + i0 + ii];
                         S[ii] = fmaf(f, S[ii], (1.0f - f) * vj);
                         o = fmaf(S[ii], qs[tt * D + i0 + ii], o);
-                        if (mode == LOCAL) P[ii] *= f;
+
                     }
                 }
                 part[(tt * DS + s) * V + j] = o;
+            }
+        }
+        if (mode == LOCAL) {                                 // (channel i stays with the same thread in every round)
+            for (int i = tid; i < D; i += nthreads) {
+                float p = pd[i];
+                for (int tt = 0; tt < nt; ++tt) p *= fs[tt * D + i];
+                pd[i] = p;
             }
         }
         __syncthreads();
@@ -121,8 +126,10 @@ hgrn2_scan_kernel(const float* __restrict__ proj, int stride, int q_off, int f_o
         for (int ii = 0; ii < DPT; ++ii)
             if (i0 + ii < D) {
                 st[(size_t)(i0 + ii) * V + j] = S[ii];
-                if (mode == LOCAL && j == 0) decay[i0 + ii] = P[ii];
             }
+    }
+    if (mode == LOCAL) {
+        for (int i = tid; i < D; i += nthreads) decay[i] = pd[i];
     }
 }
 
@@ -157,7 +164,7 @@ int launch(const float* proj, int stride, int q_off, int f_off, int v_off, const
            const int* entry_chunk0, int any_short, cudaStream_t stream) {
     const int DS = (D + DPT - 1) / DPT;
     const int threads = ((V * DS + 31) / 32) * 32;
-    const size_t smem = (size_t)TT * (2 * D + V + DS * V) * sizeof(float);
+    const size_t smem = ((size_t)TT * (2 * D + V + DS * V) + D) * sizeof(float);
     auto kern = hgrn2_scan_kernel<T, DPT>;
     if (smem > 48 * 1024) {
         INFERO_REQUIRE(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess,

@@ -1,8 +1,8 @@
 // Mixture of experts: routing, and the experts of few tokens.
 //
-// route: per token the router's logits z = Wr h in 32-bit, the `top` largest (lowest index wins a tie),
-//   their weights = softmax over the chosen logits only; optionally the gate of a shared expert,
-//   sigmoid(w_sg . h).  One warp per token.
+// select: from the router's logits z = Wr h (a product with 32-bit sums, made by the caller), per token the `top`
+//   largest (lowest index wins a tie), their weights = softmax over the chosen logits only; optionally the gate of a
+//   shared expert, the sigmoid of one more column of that product.  One warp per token.
 // experts of few tokens (a weight-streaming path; every (token, choice) reads its expert's rows):
 //   up:   act[t, c, j] = silu(Wg_e[j] . h_t) * (Wu_e[j] . h_t),  e = choice c of token t; one warp per j
 //   down: y[t, i] = sum_c weight[t, c] * (Wd_e[i] . act[t, c]) (+ gate_t * shared[t, i]); one warp per i,
@@ -17,31 +17,44 @@ constexpr int RWARPS = 4;
 constexpr int MAX_E = 512;
 constexpr int MAX_TOP = 32;
 
-template <typename T>
-__device__ __forceinline__ float warp_dot(const T* __restrict__ a, const T* __restrict__ b, int n, int lane) {
+__device__ __forceinline__ float warp_dot(const float* __restrict__ a, const float* __restrict__ b, int n, int lane) {
     float s = 0.f;
-    for (int i = lane; i < n; i += 32) s = fmaf(to_f32(a[i]), to_f32(b[i]), s);
+    for (int i = lane; i < n; i += 32) s = fmaf(a[i], b[i], s);
+    return warp_sum(s);
+}
+// bf16 rows that start on 16-byte boundaries and hold a multiple of 8 elements are read 16 bytes per lane
+__device__ __forceinline__ float warp_dot(const bf16* __restrict__ a, const bf16* __restrict__ b, int n, int lane) {
+    float s = 0.f;
+    if ((n & 7) == 0 && (((uintptr_t)a | (uintptr_t)b) & 15) == 0) {
+        for (int i = lane * 8; i < n; i += 256) {
+            const uint4 ua = *reinterpret_cast<const uint4*>(a + i), ub = *reinterpret_cast<const uint4*>(b + i);
+            const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ua);
+            const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&ub);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 fa = __bfloat1622float2(pa[j]), fb = __bfloat1622float2(pb[j]);
+                s = fmaf(fa.x, fb.x, s);
+                s = fmaf(fa.y, fb.y, s);
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) s = fmaf(__bfloat162float(a[i]), __bfloat162float(b[i]), s);
+    }
     return warp_sum(s);
 }
 
-template <typename T>
+// logits float32 [tokens, stride]: columns 0..E-1 are the router's logits; column gate_col (if >= 0) is the logit of
+// the shared expert's gate.
 __global__ void __launch_bounds__(RWARPS * 32)
-moe_route_kernel(const T* __restrict__ h, int h_stride, const T* __restrict__ router, const T* __restrict__ shared_gate,
-                 int* __restrict__ top_idx, float* __restrict__ top_w, float* __restrict__ gate_out,
-                 int n_tokens, int d, int E, int top) {
+moe_select_kernel(const float* __restrict__ logits, int stride, int gate_col, int* __restrict__ top_idx,
+                  float* __restrict__ top_w, float* __restrict__ gate_out, int n_tokens, int E, int top) {
     __shared__ float z[RWARPS][MAX_E];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * RWARPS + warp;
     if (t >= n_tokens) return;
-    const T* hr = h + (size_t)t * h_stride;
-    for (int e = 0; e < E; ++e) {
-        const float v = warp_dot(router + (size_t)e * d, hr, d, lane);
-        if (lane == 0) z[warp][e] = v;
-    }
-    if (shared_gate) {
-        const float v = warp_dot(shared_gate, hr, d, lane);
-        if (lane == 0) gate_out[t] = 1.0f / (1.0f + expf(-v));
-    }
+    const float* zr = logits + (size_t)t * stride;
+    for (int e = lane; e < E; e += 32) z[warp][e] = zr[e];
+    if (gate_col >= 0 && lane == 0) gate_out[t] = 1.0f / (1.0f + expf(-zr[gate_col]));
     __syncwarp();
     float first = 0.f, mine = 0.f, sum = 0.f;
     int mine_e = 0;
@@ -116,19 +129,14 @@ moe_down_kernel(const T* __restrict__ act, const T* __restrict__ down, const int
 
 extern "C" {
 
-int infero_moe_route(const void* h, int h_stride, const void* router, const void* shared_gate, int dtype, int* top_idx,
-                     float* top_w, float* gate_out, int n_tokens, int d, int E, int top, cudaStream_t stream) {
+int infero_moe_select(const float* logits, int stride, int gate_col, int* top_idx, float* top_w, float* gate_out,
+                      int n_tokens, int E, int top, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     INFERO_REQUIRE(E >= 1 && E <= MAX_E && top >= 1 && top <= E && top <= MAX_TOP,
-                   "moe route: %d experts (at most %d), top %d (at most %d)", E, MAX_E, top, MAX_TOP);
-    const unsigned blocks = (n_tokens + RWARPS - 1) / RWARPS;
-    if (dtype == INFERO_F32)
-        moe_route_kernel<float><<<blocks, RWARPS * 32, 0, stream>>>((const float*)h, h_stride, (const float*)router,
-            (const float*)shared_gate, top_idx, top_w, gate_out, n_tokens, d, E, top);
-    else
-        moe_route_kernel<bf16><<<blocks, RWARPS * 32, 0, stream>>>((const bf16*)h, h_stride, (const bf16*)router,
-            (const bf16*)shared_gate, top_idx, top_w, gate_out, n_tokens, d, E, top);
-    return infero_check_launch("moe_route");
+                   "moe select: %d experts (at most %d), top %d (at most %d)", E, MAX_E, top, MAX_TOP);
+    moe_select_kernel<<<(n_tokens + RWARPS - 1) / RWARPS, RWARPS * 32, 0, stream>>>(logits, stride, gate_col, top_idx, top_w,
+                                                                                  gate_out, n_tokens, E, top);
+    return infero_check_launch("moe_select");
 }
 
 // act: [tokens * top, ff] of dtype (scratch); y float32 [tokens, d]; shared float32 [tokens, d] or null.

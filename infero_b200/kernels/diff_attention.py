@@ -41,8 +41,24 @@ def prefill(q, out, k_cache, v_cache, table, entry_q_start, entry_q_len, entry_p
         c_int(window or 0), c_float(scale), c_float(lam), c_float(eps), c_float(out_scale), _stream()))
 
 
-def paged_diff_attention(ctx, q, out, kv, table, H, G, D, V, window, scale, lam, eps, out_scale) -> None:
-    """q [T, H*2*D] (normed, rotated), out [T, H*V]; keys [pages, G, page, 2 D], values [pages, G, page, V]."""
+def as_plain_heads(dtype, D: int, V: int, page_size: int) -> bool:
+    """Can the kernels for ordinary heads run this layer?  Where a value is as wide as a key row (V = 2 D), every map
+    is an ordinary head of width V over the same cache once its query is padded with zeros in the other map's
+    columns: bf16 steps then take the engine's split-context decode kernel and its tensor-core prompt kernels (2 H
+    heads over G kv heads) and a small kernel that combines the maps."""
+    from .attention import mma_supported
+    return dtype == torch.bfloat16 and V == 2 * D and mma_supported(V, page_size)
+
+
+def paged_diff_attention(ctx, q, out, kv, table, H, G, D, V, window, scale, lam, eps, out_scale, q_padded: bool = False) -> None:
+    """q [T, H*2*D] (normed, rotated; [T, 2 H * 2 D] when ``q_padded``, see ``as_plain_heads``), out [T, H*V];
+    keys [pages, G, page, 2 D], values [pages, G, page, V]."""
+    if q_padded:
+        from .attention import paged_attention
+        maps = torch.empty((q.shape[0], 2 * H * V), dtype=q.dtype, device=q.device)
+        paged_attention(ctx, q, maps, kv, table, 2 * H, G, V, window, scale)
+        L.diff_combine(maps, out, H, V, lam, eps, out_scale)
+        return
     n_dec, _, _, tiles_64 = _batch_shape(ctx)
     E, T = ctx.n_entries, q.shape[0]
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == kv.k.dtype == kv.v.dtype

@@ -42,27 +42,54 @@ def gated_scalar_norm_add(x: torch.Tensor, y: torch.Tensor, gate: Optional[torch
 def hgrn2_scan(proj: torch.Tensor, q_off: int, f_off: int, v_off: int, f_bias: torch.Tensor, lower: torch.Tensor,
                out_w: torch.Tensor, eps: float, state: torch.Tensor, entry_q_start: torch.Tensor,
                entry_q_len: torch.Tensor, entry_slot: torch.Tensor, out: torch.Tensor, n_entries: int,
-               H: int, D: int, V: int) -> None:
+               H: int, D: int, V: int, q_lens=None) -> None:
     """The recurrence of every request of the step over its new tokens; see csrc/hgrn2.cu.
-    proj float32 [T, >= ...] (row stride free); state float32 [slots, H, D, V]; out [T, H*V]."""
+    proj float32 [T, >= ...] (row stride free); state float32 [slots, H, D, V]; out [T, H*V].
+    ``q_lens``: the host's copy of ``entry_q_len``; with it, long portions run by chunks side by side."""
     assert proj.dtype == torch.float32 and proj.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
     assert tuple(state.shape[1:]) == (H, D, V) and out.shape[1] == H * V and out.stride(1) == 1
     _f32(f_bias, "f_bias"), _f32(lower, "lower"), _f32(out_w, "out_w")
+    max_chunks, any_short, chunk_state, chunk_decay, chunk0 = 0, 1, None, None, None
+    if q_lens is not None:
+        chunk, long_ = _hgrn2_sizes()
+        counts = [(-(-int(n) // chunk) if int(n) >= long_ else 0) for n in q_lens]
+        max_chunks = max(counts, default=0)
+        if max_chunks:
+            any_short = int(any(c == 0 for c in counts))
+            firsts, total = [], 0
+            for c in counts:
+                firsts.append(total)
+                total += c
+            chunk0 = torch.tensor(firsts, dtype=torch.int32).to(proj.device, non_blocking=True)
+            chunk_state = torch.empty((total, H, D, V), dtype=torch.float32, device=proj.device)
+            chunk_decay = torch.empty((total, H, D), dtype=torch.float32, device=proj.device)
     _check(lib().infero_hgrn2_scan(_ptr(proj), c_int(proj.stride(0)), c_int(q_off), c_int(f_off), c_int(v_off),
                                    _ptr(f_bias), _ptr(lower), _ptr(out_w), c_float(eps), _ptr(state),
                                    _ptr(_i32(entry_q_start, "entry_q_start")), _ptr(_i32(entry_q_len, "entry_q_len")),
                                    _ptr(_i32(entry_slot, "entry_slot")), _ptr(out), c_int(_dt(out)), c_int(out.stride(0)),
-                                   c_int(n_entries), c_int(H), c_int(D), c_int(V), _stream()))
+                                   c_int(n_entries), c_int(H), c_int(D), c_int(V), c_int(max_chunks), _ptr(chunk_state),
+                                   _ptr(chunk_decay), _ptr(chunk0), c_int(any_short), _stream()))
+
+
+_HGRN2_SIZES = []
+
+
+def _hgrn2_sizes():
+    if not _HGRN2_SIZES:
+        _HGRN2_SIZES.extend([int(lib().infero_hgrn2_chunk()), int(lib().infero_hgrn2_long())])
+    return _HGRN2_SIZES
 
 
 def qkv_prepare(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int, conv_state: Optional[torch.Tensor],
                 q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
                 inv_freq: Optional[torch.Tensor], positions, tok_entry, entry_q_start, entry_slot, block_table,
                 q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int, n_q_units: int,
-                n_k_units: int, G: int, D: int, V: int, write_cache: bool = True) -> None:
+                n_k_units: int, G: int, D: int, V: int, write_cache: bool = True, q_pad: bool = False) -> None:
     """Convolution over time, per-map RMS norm, adjacent-pair rotary, q to ``q_out``, k and v to their pages;
-    see csrc/diff_attention.cu."""
+    see csrc/diff_attention.cu.  ``q_pad``: q_out is [T, n_q_units * 2 D], every map a query as wide as a key row
+    with zeros in the other map's columns."""
     T = q_out.shape[0]
+    assert q_out.shape[1] == n_q_units * D * (2 if q_pad else 1)
     assert proj.dtype == torch.float32 and proj.stride(1) == 1 and q_out.stride(1) == 1
     assert k_cache.dtype == q_out.dtype == v_cache.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert k_cache.shape[-1] == (n_k_units // G) * D and v_cache.shape[-1] == V and k_cache.shape[1] == G
@@ -75,7 +102,16 @@ def qkv_prepare(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int, c
         _ptr(_i32(entry_slot, "entry_slot")), _ptr(_i32(block_table, "block_table")), c_int(block_table.shape[1]),
         _ptr(q_out), c_int(q_out.stride(0)), _ptr(k_cache), _ptr(v_cache), c_int(_dt(q_out)), c_int(page_size),
         c_int(T), c_int(n_q_units), c_int(n_k_units), c_int(G), c_int(D), c_int(V), c_int(1 if write_cache else 0),
-        _stream()))
+        c_int(1 if q_pad else 0), _stream()))
+
+
+def diff_combine(maps: torch.Tensor, out: torch.Tensor, H: int, V: int, lam: float, eps: float, out_scale: float) -> None:
+    """maps [T, H*2*V] (per head the two maps' attention results) -> out [T, H*V]: a1 - lam a2, weightless RMS norm
+    over V, times out_scale."""
+    T = maps.shape[0]
+    assert maps.dtype == out.dtype and maps.stride(1) == 1 and out.stride(1) == 1 and maps.shape[1] == 2 * H * V
+    _check(lib().infero_diff_combine(_ptr(maps), c_int(maps.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(_dt(out)),
+                                     c_int(T), c_int(H), c_int(V), c_float(lam), c_float(eps), c_float(out_scale), _stream()))
 
 
 def conv_state_update(proj: torch.Tensor, conv_state: torch.Tensor, taps: int, entry_q_start, entry_q_len,
@@ -103,19 +139,17 @@ def diff_attention_generic(q, out, k_cache, v_cache, block_table, tok_entry, pos
         c_int(window or 0), c_float(scale), c_float(lam), c_float(eps), c_float(out_scale), _stream()))
 
 
-def moe_route(h: torch.Tensor, router: torch.Tensor, shared_gate: Optional[torch.Tensor], top: int):
-    """(top_idx int32 [T, top], top_w float32 [T, top], gate float32 [T] or None); see csrc/moe.cu."""
-    T, d = h.shape
-    E = router.shape[0]
-    assert h.stride(1) == 1 and router.dtype == h.dtype and router.is_contiguous() and router.shape[1] == d
-    idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
-    w = torch.empty((T, top), dtype=torch.float32, device=h.device)
-    gate = None
-    if shared_gate is not None:
-        assert shared_gate.dtype == h.dtype and shared_gate.numel() == d and shared_gate.is_contiguous()
-        gate = torch.empty(T, dtype=torch.float32, device=h.device)
-    _check(lib().infero_moe_route(_ptr(h), c_int(h.stride(0)), _ptr(router), _ptr(shared_gate), c_int(_dt(h)),
-                                  _ptr(idx), _ptr(w), _ptr(gate), c_int(T), c_int(d), c_int(E), c_int(top), _stream()))
+def moe_select(logits: torch.Tensor, E: int, top: int, gate_col: int = -1):
+    """From float32 logits [T, >= E] (row stride free): (top_idx int32 [T, top], top_w float32 [T, top], gate float32
+    [T] or None): the ``top`` largest of the first E columns, softmax over those alone; gate = sigmoid(column
+    ``gate_col``).  See csrc/moe.cu."""
+    T = logits.shape[0]
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[1] >= E
+    idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    gate = torch.empty(T, dtype=torch.float32, device=logits.device) if gate_col >= 0 else None
+    _check(lib().infero_moe_select(_ptr(logits), c_int(logits.stride(0)), c_int(gate_col), _ptr(idx), _ptr(w), _ptr(gate),
+                                   c_int(T), c_int(E), c_int(top), _stream()))
     return idx, w, gate
 
 
@@ -144,13 +178,45 @@ def moe_experts_grouped(h, gate_up, down, top_idx, top_w, shared, shared_gate, y
     assert gate_up.is_contiguous() and down.is_contiguous() and tuple(down.shape) == (E, d, ff)
     assert y.dtype == torch.float32 and y.is_contiguous() and y.shape == (T, d) and h.stride(1) == 1
     tiles = int(lib().infero_moe_grouped_tiles(c_int(T * top), c_int(E)))
+    R = tiles * int(lib().infero_moe_grouped_tile_rows(c_int(T * top), c_int(E)))
     dev = h.device
-    ints = torch.empty(2 * tiles * 64 + tiles, dtype=torch.int32, device=dev)
-    sorted_pair, a_rows, tile_expert = ints[:tiles * 64], ints[tiles * 64:2 * tiles * 64], ints[2 * tiles * 64:]
-    act = torch.empty((tiles * 64, ff), dtype=torch.bfloat16, device=dev)
+    ints = torch.empty(2 * R + tiles, dtype=torch.int32, device=dev)
+    sorted_pair, a_rows, tile_expert = ints[:R], ints[R:2 * R], ints[2 * R:]
+    act = torch.empty((R, ff), dtype=torch.bfloat16, device=dev)
     part = torch.empty((T * top, d), dtype=torch.float32, device=dev)
     _check(lib().infero_moe_experts_grouped(_ptr(h), c_int(h.stride(0)), _ptr(gate_up), _ptr(down),
                                             _ptr(_i32(top_idx, "top_idx")), _ptr(_f32(top_w, "top_w")),
                                             _ptr(_f32(shared, "shared")), _ptr(_f32(shared_gate, "shared_gate")),
                                             _ptr(sorted_pair), _ptr(a_rows), _ptr(tile_expert), _ptr(act), _ptr(part),
                                             _ptr(y), c_int(T), c_int(d), c_int(ff), c_int(E), c_int(top), _stream()))
+
+
+def moe_experts_tc(h, gate_up, down, top_idx, top_w, shared, shared_gate, y) -> None:
+    """The same result by grouped products on the tcgen05 kernel: the tokens' rows are copied into expert order in
+    tiles of 128 rows, two grouped products (the first with the SwiGLU epilogue) run over them, and the rows of a
+    token's choices are added up in ascending order; see csrc/moe_grouped.cu and ``infero_gemm_tc_grouped``."""
+    from .tc_gemm import sm_count
+    T, d = h.shape
+    E, ff2, _ = gate_up.shape
+    ff, top = ff2 // 2, top_idx.shape[1]
+    assert h.dtype == torch.bfloat16 and gate_up.dtype == torch.bfloat16 and down.dtype == torch.bfloat16
+    assert gate_up.is_contiguous() and down.is_contiguous() and tuple(down.shape) == (E, d, ff)
+    assert y.dtype == torch.float32 and y.is_contiguous() and y.shape == (T, d) and h.stride(1) == 1
+    tiles = int(lib().infero_moe_tc_tiles(c_int(T * top), c_int(E)))
+    R, dev = tiles * 128, h.device
+    ints = torch.empty(2 * R + tiles + T * top, dtype=torch.int32, device=dev)
+    sorted_pair, a_rows, tile_expert, pair_row = ints[:R], ints[R:2 * R], ints[2 * R:2 * R + tiles], ints[2 * R + tiles:]
+    xs = torch.empty((R, d), dtype=torch.bfloat16, device=dev)
+    _check(lib().infero_moe_tc_prepare(_ptr(h), c_int(h.stride(0)), _ptr(_i32(top_idx, "top_idx")), _ptr(sorted_pair),
+                                       _ptr(a_rows), _ptr(tile_expert), _ptr(pair_row), _ptr(xs), c_int(T), c_int(d),
+                                       c_int(E), c_int(top), _stream()))
+    act = torch.empty((R, ff), dtype=torch.bfloat16, device=dev)
+    sms = sm_count(dev)
+    _check(lib().infero_gemm_tc_grouped(_ptr(xs), _ptr(gate_up), _ptr(act), c_int(1), c_int(R), c_int(2 * ff), c_int(d),
+                                        c_int(d), c_int(ff), _ptr(tile_expert), c_int(E), c_int(sms), _stream()))
+    rows = torch.empty((R, d), dtype=torch.float32, device=dev)
+    _check(lib().infero_gemm_tc_grouped(_ptr(act), _ptr(down), _ptr(rows), c_int(0), c_int(R), c_int(d), c_int(ff),
+                                        c_int(ff), c_int(d), _ptr(tile_expert), c_int(E), c_int(sms), _stream()))
+    _check(lib().infero_moe_tc_combine(_ptr(rows), _ptr(pair_row), _ptr(_f32(top_w, "top_w")), _ptr(_f32(shared, "shared")),
+                                       _ptr(_f32(shared_gate, "shared_gate")), _ptr(y), c_int(T), c_int(d), c_int(top),
+                                       _stream()))

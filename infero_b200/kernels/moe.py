@@ -1,8 +1,10 @@
 """Choice of kernel for the experts of a mixture-of-experts feed-forward.
 
 Few tokens: every (token, choice) streams the rows of its expert (bound by the bytes of the chosen experts).
-Many tokens on the bf16 path: grouped tensor-core products over the pairs sorted by expert, so an expert's
-matrices are read once per 64 rows.  The 32-bit path always streams."""
+More tokens on the bf16 path: grouped tensor-core products over the (token, choice) pairs sorted by expert, so an
+expert's matrices are read once per tile of rows: on the tcgen05 product kernel (tiles of 128 rows) when an expert
+gets about a tile's worth of pairs, on a warp-level kernel with tiles of 64 rows below that.  The 32-bit path
+always streams."""
 from __future__ import annotations
 
 import os
@@ -12,14 +14,21 @@ import torch
 from . import layer_ops as L
 
 GROUPED_FROM = int(os.environ.get("INFERO_MOE_GROUPED_FROM", "5"))     # tokens from which the grouped path runs
+TC_PAIRS_PER_EXPERT = int(os.environ.get("INFERO_MOE_TC_FROM", "96"))  # pairs per expert from which tcgen05 tiles pay
 
 
 def experts(h, gate_up, down, top_idx, top_w, shared, shared_gate, y) -> None:
     T, d = h.shape
     ff = gate_up.shape[1] // 2
-    if (h.dtype == torch.bfloat16 and T >= GROUPED_FROM and d % 8 == 0 and ff % 8 == 0 and h.stride(0) % 8 == 0
-            and h.data_ptr() % 16 == 0):
-        L.moe_experts_grouped(h, gate_up, down, top_idx, top_w, shared, shared_gate, y)
+    E, top = gate_up.shape[0], top_idx.shape[1]
+    # streaming reads an expert once per pair that chose it, the grouped products once per tile of its pairs: with no
+    # more pairs than experts streaming reads no more than they do
+    if (h.dtype == torch.bfloat16 and T >= GROUPED_FROM and T * top > E and d % 8 == 0 and ff % 8 == 0
+            and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0):
+        if T * top >= TC_PAIRS_PER_EXPERT * E and gate_up.data_ptr() % 16 == 0 and down.data_ptr() % 16 == 0:
+            L.moe_experts_tc(h, gate_up, down, top_idx, top_w, shared, shared_gate, y)
+        else:
+            L.moe_experts_grouped(h, gate_up, down, top_idx, top_w, shared, shared_gate, y)
         return
     # the streaming kernels index (token, choice) pairs by a grid dimension of at most 65,535
     step = max(1, 65535 // top_idx.shape[1])

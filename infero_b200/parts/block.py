@@ -88,8 +88,8 @@ class GatedPostNormBlock(Part):
         for n in (self.mixer_norm, self.ffn_norm):
             if n is not None and not hasattr(n, "scalar"):
                 raise ValueError("a gated post-norm block takes norms with a single stored number")
-        self.gates = [None, None]            # Linear of each half's gate
-        self.gate_bias = [None, None]
+        self.gates = [None, None]            # Linear of each half's gate, or "stacked": the gate's rows ride on the
+        self.gate_bias = [None, None]        # sublayer's own input product (parts with ``append_rows``)
 
     def parts(self):
         return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None]
@@ -116,7 +116,12 @@ class GatedPostNormBlock(Part):
         for i, name in enumerate(self._gate_names()):
             if name:
                 full = f"{self.spec.prefix}.{name}"
-                self.gates[i] = Linear(tensors[full], None, full)
+                part = self.mixer if i == 0 else self.ffn
+                if hasattr(part, "append_rows"):
+                    part.append_rows(tensors[full])
+                    self.gates[i] = "stacked"
+                else:
+                    self.gates[i] = Linear(tensors[full], None, full)
                 self.gate_bias[i] = tensors[full + self.spec.gate_bias_suffix].float().contiguous()
 
     def _input(self, ctx, x):
@@ -134,7 +139,10 @@ class GatedPostNormBlock(Part):
 
     def _half(self, ctx, x, h, y, i, norm):
         from ..kernels import layer_ops as L
-        g = self.gates[i].forward(h, out_dtype=torch.float32) if self.gates[i] is not None else None
+        if self.gates[i] == "stacked":
+            g = ctx.extra_product                # left by the sublayer that just ran
+        else:
+            g = self.gates[i].forward(h, out_dtype=torch.float32) if self.gates[i] is not None else None
         h_next = torch.empty(x.shape, dtype=ctx.act_dtype, device=x.device) if ctx.act_dtype != torch.float32 else None
         L.gated_scalar_norm_add(x, y, g, self.gate_bias[i], norm.scalar, norm.spec.eps, h_next)
         return x if h_next is None else h_next

@@ -69,7 +69,9 @@ class DiffAttention(Mixer):
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         s = self.spec
-        self.qkv = Linear(torch.cat([tensors[self._n(r)] for r in ("q", "k", "v")], dim=0), None, f"{self.prefix}.qkv")
+        self._rows = torch.cat([tensors[self._n(r)] for r in ("q", "k", "v")], dim=0)
+        self.qkv = Linear(self._rows, None, f"{self.prefix}.qkv")
+        self.extra = None
         self.out = Linear(tensors[self._n("o")], None, self._n("o"))
         f32 = lambda r: tensors[self._n(r, False)].float().contiguous()          # noqa: E731
         self.q_norm = f32("q_norm") if s.qk_norm else None
@@ -78,24 +80,32 @@ class DiffAttention(Mixer):
         v = {r: tensors[self._n(r, False)].double().cpu() for r in ("lq1", "lk1", "lq2", "lk2")}
         self.lam = math.exp(float((v["lq1"] * v["lk1"]).sum())) - math.exp(float((v["lq2"] * v["lk2"]).sum())) + s.diff
 
+    def append_rows(self, weight: torch.Tensor) -> None:
+        """Stack more rows of the layer's input product behind q, k and v; their result is left in
+        ``ctx.extra_product`` (float32 [T, rows]) by ``forward``."""
+        self.qkv = Linear(torch.cat([self._rows, weight], dim=0), None, f"{self.prefix}.qkv")
+        self.extra = (self._rows.shape[0], weight.shape[0])
+
     def forward(self, ctx, h, slot):
         s = self.spec
         H, G, D, V = self.H, self.G, self.D, self.V
         T = h.shape[0]
-        proj = self.qkv.forward(h, out_dtype=torch.float32)                # [T, Cq + Ck + Cv]
+        proj = self.qkv.forward(h, out_dtype=torch.float32)                # [T, Cq + Ck + Cv (+ stacked rows)]
+        ctx.extra_product = proj[:, self.extra[0]:self.extra[0] + self.extra[1]] if self.extra else None
         kv = ctx.kv_cache(slot.cache)
         table = ctx.block_table(kv.group)
         state = ctx.state(slot.cache) if self.taps > 1 else None
-        q = torch.empty((T, self.Cq), dtype=h.dtype, device=h.device)
+        from ..kernels import diff_attention as A
+        padded = A.as_plain_heads(h.dtype, D, V, kv.page_size) and kv.k.is_contiguous() and kv.v.is_contiguous()
+        q = torch.empty((T, self.Cq * (2 if padded else 1)), dtype=h.dtype, device=h.device)
         inv = self.rope.inv_freq(h.device) if self.rope is not None else None
         L.qkv_prepare(proj, self.conv_w, self.taps, state, self.q_norm, self.k_norm, s.norm_eps, inv, ctx.positions,
                       ctx.tok_entry, ctx.entry_q_start, ctx.entry_slot, table, q, kv.k, kv.v, kv.page_size,
-                      2 * H, 2 * G, G, D, V, write_cache=slot.write_cache)
+                      2 * H, 2 * G, G, D, V, write_cache=slot.write_cache, q_pad=padded)
         if state is not None:
             L.conv_state_update(proj, state, self.taps, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_slot,
                                 ctx.n_entries, self.Cq + self.Ck + self.Cv)
         attn = torch.empty((T, H * V), dtype=h.dtype, device=h.device)
-        from ..kernels import diff_attention as A
         A.paged_diff_attention(ctx, q, attn, kv, table, H, G, D, V, s.window, s.scale, self.lam, s.norm_eps,
-                               1.0 - s.diff)
+                               1.0 - s.diff, q_padded=padded)
         return self.out.forward(attn, residual=True, out_dtype=torch.float32)

@@ -45,18 +45,27 @@ class Hgrn2Mixer(Mixer):
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         w = torch.cat([tensors[self._n(r)] for r in ("q", "f", "v")], dim=0)
+        self._rows = w
         self.qfv = Linear(w, None, f"{self.prefix}.qfv")
+        self.extra = None
         self.out = Linear(tensors[self._n("o")], None, self._n("o"))
         self.f_bias = tensors[self._n("f_bias", False)].float().contiguous()
         self.lower = tensors[self._n("lower", False)].float().contiguous()
         self.out_norm = tensors[self._n("out_norm", False)].float().contiguous()
 
+    def append_rows(self, weight: torch.Tensor) -> None:
+        """Stack more rows of the layer's input product behind q, f and v; their result is left in
+        ``ctx.extra_product`` (float32 [T, rows]) by ``forward``."""
+        self.qfv = Linear(torch.cat([self._rows, weight], dim=0), None, f"{self.prefix}.qfv")
+        self.extra = (self._rows.shape[0], weight.shape[0])
+
     def forward(self, ctx, h, slot):
         H, D, V = self.H, self.D, self.V
         T = h.shape[0]
-        proj = self.qfv.forward(h, out_dtype=torch.float32)              # [T, 2 H D + H V]
+        proj = self.qfv.forward(h, out_dtype=torch.float32)              # [T, 2 H D + H V (+ stacked rows)]
+        ctx.extra_product = proj[:, self.extra[0]:self.extra[0] + self.extra[1]] if self.extra else None
         o = torch.empty((T, H * V), dtype=h.dtype, device=h.device)
         L.hgrn2_scan(proj, 0, H * D, 2 * H * D, self.f_bias, self.lower, self.out_norm, self.spec.norm_eps,
                      ctx.state(slot.cache), ctx.entry_q_start, ctx.entry_q_len, ctx.entry_slot, o, ctx.n_entries,
-                     H, D, V)
+                     H, D, V, q_lens=None if ctx.decode_only else ctx.h_q_len)
         return self.out.forward(o, residual=True, out_dtype=torch.float32)

@@ -9,6 +9,7 @@ from .. import kernels as K
 from ..config.spec import FeedForwardSpec
 from ..kernels import layer_ops as L
 from .base import FeedForward, TensorDecl
+from .linear import Linear
 from .mlp import SwiGluMlp
 
 
@@ -55,15 +56,28 @@ class MoeSwiGlu(FeedForward):
         u = torch.stack([tensors[self._expert(e, "up")] for e in range(self.E)])
         self.gate_up = torch.stack([g, u], dim=2).reshape(self.E, 2 * self.ff, self.spec.hidden).contiguous()
         self.down = torch.stack([tensors[self._expert(e, "down")] for e in range(self.E)]).contiguous()
-        self.router = tensors[self._n("router")].contiguous()
-        self.shared_gate = None
+        # one product gives the router's logits, the logit of the shared expert's gate and whatever rows the block
+        # stacks behind (``append_rows``)
+        rows = [tensors[self._n("router")]]
         if self.shared is not None:
             self.shared.bind(tensors)
-            self.shared_gate = tensors[self._n("shared_gate")].reshape(-1).contiguous()
+            rows.append(tensors[self._n("shared_gate")].reshape(1, -1))
+        self._route_rows = torch.cat(rows, dim=0)
+        self.route = Linear(self._route_rows, None, f"{self.prefix}.route")
+        self.extra = None
+
+    def append_rows(self, weight: torch.Tensor) -> None:
+        """Stack more rows of the layer's input product behind the router's; their result is left in
+        ``ctx.extra_product`` (float32 [T, rows]) by ``forward``."""
+        at = self._route_rows.shape[0]
+        self.route = Linear(torch.cat([self._route_rows, weight], dim=0), None, f"{self.prefix}.route")
+        self.extra = (at, weight.shape[0])
 
     def forward(self, ctx, h):
         T, d = h.shape
-        idx, w, gate = L.moe_route(h, self.router, self.shared_gate, self.top)
+        z = self.route.forward(h, out_dtype=torch.float32)
+        idx, w, gate = L.moe_select(z, self.E, self.top, self.E if self.shared is not None else -1)
+        ctx.extra_product = z[:, self.extra[0]:self.extra[0] + self.extra[1]] if self.extra else None
         shared = None
         if self.shared is not None:
             shared = self.shared.forward(ctx, h)

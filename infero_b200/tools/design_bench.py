@@ -51,6 +51,19 @@ class _Timer:
 
     def __call__(self, fn, reps=7, warmup=3, setup=None):
         torch = self.torch
+        if setup is None:
+            # a kernel alone: replayed from a captured graph, so that the host's share of a launch is not timed
+            fn()
+            torch.cuda.synchronize()
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    from infero_b200 import kernels as K
+                    with K.stream_scope():
+                        fn()
+                fn = graph.replay
+            except Exception:                          # noqa: BLE001  (something in fn cannot be captured: time it as it is)
+                torch.cuda.synchronize()
         times = []
         for i in range(warmup + reps):
             if setup:
@@ -123,6 +136,7 @@ def time_kernels(z, T, context, batch, timer, peaks):
     import torch
     from infero_b200 import kernels as K
     from infero_b200.kernels import attention as A, diff_attention as DA, layer_ops as L, moe as M, tc_gemm
+    from infero_b200.parts.linear import Linear
     dev, bf = "cuda:0", torch.bfloat16
     d, H, G, D, V = z["width"], z["heads"], z["kv"], z["dim"], z["vdim"]
     E, top, ff = z["experts"], z["top"], z["ff"]
@@ -163,11 +177,12 @@ def time_kernels(z, T, context, batch, timer, peaks):
         n = ctx.n_tokens
         kd, vd = rnd(pages, G, 16, 2 * D), rnd(pages, G, 16, V)
         kv = types.SimpleNamespace(k=kd, v=vd, page_size=16)
-        q, out = rnd(n, 2 * H * D), torch.empty(n, H * V, dtype=bf, device=dev)
+        padded = DA.as_plain_heads(bf, D, V, 16)
+        q, out = rnd(n, 2 * H * D * (2 if padded else 1)), torch.empty(n, H * V, dtype=bf, device=dev)
         keys = sum(p + (n_ + 1) / 2 * 1 for p, n_ in zip(pos0, q_lens)) if label == "decode" else T / 2
         fl = 2.0 * H * (2 * D + 2 * V) * (T * T / 2 if label == "prefill" else batch * context)
         by = 2.0 * G * (2 * D + V) * (T if label == "prefill" else batch * context) + 2.0 * n * (2 * H * D + H * V)
-        ms = timer(lambda: DA.paged_diff_attention(ctx, q, out, kv, table, H, G, D, V, None, D ** -0.5, 0.4, 1e-5, 0.5))
+        ms = timer(lambda: DA.paged_diff_attention(ctx, q, out, kv, table, H, G, D, V, None, D ** -0.5, 0.4, 1e-5, 0.5, q_padded=padded))
         note(f"diff_attention_{label}", ms, by, fl)
         # the built-in attention with a head as wide as both maps (2 D) and values of the same width
         Dq = 2 * D
@@ -178,6 +193,10 @@ def time_kernels(z, T, context, batch, timer, peaks):
         ms = timer(lambda: A.attention_any(q2, out2, k2, v2, table, ctx.tok_entry, ctx.positions, H, G, Dq, 16, None, Dq ** -0.5,
                                            ctx.h_q_len, ctx.h_pos0, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_pos0))
         note(f"gqa_attention_{label}", ms, by2, fl2)
+        if label == "prefill":      # the built-in kernel on the warp-level tensor cores (what head sizes other than 64 and 128 get)
+            ms = timer(lambda: A.prefill(q2, out2, k2, v2, table, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_pos0, 1, 0,
+                                         -(-T // 64), H, G, Dq, 16, None, Dq ** -0.5))
+            note("gqa_attention_prefill_mma_sync", ms, by2, fl2)
 
     # ---- the recurrence ------------------------------------------------------------------------------------------
     for label, q_lens in (("prefill", [T]), ("decode", [1] * batch)):
@@ -199,8 +218,9 @@ def time_kernels(z, T, context, batch, timer, peaks):
     for label, n in (("prefill", T), ("decode", batch)):
         h = rnd(n, d)
         y = torch.empty(n, d, device=dev)
-        idx, w, _ = L.moe_route(h, router, None, top)
-        ms = timer(lambda: L.moe_route(h, router, None, top))
+        route = Linear(router)
+        idx, w, _ = L.moe_select(route.forward(h, out_dtype=torch.float32), E, top)
+        ms = timer(lambda: L.moe_select(route.forward(h, out_dtype=torch.float32), E, top))
         note(f"moe_route_{label}", ms, 2.0 * (n * d + E * d))
         used = min(E, n * top)
         ms = timer(lambda: M.experts(h, gu, dn, idx, w, None, None, y))

@@ -40,14 +40,17 @@ def test_gated_norm_add_kernel():
     assert _rel(xd, x.double() + 1.3 * PV.unit_rms(y.double(), 1e-5)) < 2e-6
 
 
-@pytest.mark.parametrize("H,D,V", [(2, 16, 32), (1, 12, 20), (3, 48, 64), (2, 128, 128), (1, 200, 40)])
-def test_hgrn2_scan_kernel(H, D, V):
+@pytest.mark.parametrize("H,D,V,lens", [(2, 16, 32, [9, 1, 20]), (1, 12, 20, [9, 1, 20]), (3, 48, 64, [9, 1, 20]),
+                                        (2, 128, 128, [9, 1, 20]), (1, 200, 40, [9, 1, 20]),
+                                        (2, 16, 32, [515, 1, 260]), (1, 48, 64, [130, 700, 512])])
+def test_hgrn2_scan_kernel(H, D, V, lens):
     """Three requests of unequal length in one launch, then continued from their state slots in a second one
-    in another order; slots are not the entries' indices."""
+    in another order; slots are not the entries' indices.  Portions of 512 tokens and more run by chunks side by
+    side, beside short ones that run whole."""
     from infero_b200.kernels import layer_ops as L
     g = torch.Generator().manual_seed(H * 100 + D)
     d = 24
-    lens, slots = [9, 1, 20], [4, 0, 2]
+    slots = [4, 0, 2]
     wq, wf, wv = (torch.randn(n, d, generator=g) * 0.4 for n in (H * D, H * D, H * V))
     bf, lower, wn = torch.randn(H * D, generator=g), torch.rand(H * D, generator=g), 1 + 0.1 * torch.randn(V, generator=g)
     hs = [torch.randn(2 * n + 3, d, generator=g) for n in lens]
@@ -64,7 +67,7 @@ def test_hgrn2_scan_kernel(H, D, V):
         i32 = lambda a: torch.tensor(list(a), dtype=torch.int32, device=DEV)      # noqa: E731
         out = torch.empty(proj.shape[0], H * V, device=DEV)
         L.hgrn2_scan(proj, 0, H * D, 2 * H * D, bf.to(DEV), lower.to(DEV), wn.to(DEV), 1e-5, state, i32(qs), i32(ql),
-                     i32(slots[i] for i in order), out, len(order), H, D, V)
+                     i32(slots[i] for i in order), out, len(order), H, D, V, q_lens=ql)
         for k, i in enumerate(order):
             got[i].append(out[qs[k]:qs[k] + ql[k]].cpu())
     eye = torch.eye(H * V, dtype=torch.float64)
@@ -76,10 +79,12 @@ def test_hgrn2_scan_kernel(H, D, V):
 
 
 @pytest.mark.parametrize("dtype,E,top,d,ff,T", [("float32", 6, 2, 40, 12, 9), ("float32", 3, 3, 20, 7, 3), ("bfloat16", 8, 3, 64, 24, 150),
-                                               ("bfloat16", 5, 1, 72, 40, 70), ("bfloat16", 4, 2, 64, 16, 2)])
+                                               ("bfloat16", 5, 1, 72, 40, 70), ("bfloat16", 4, 2, 64, 16, 2), ("bfloat16", 3, 2, 64, 24, 400),
+                                               ("bfloat16", 6, 2, 136, 72, 700)])
 def test_routing_and_experts(dtype, E, top, d, ff, T):
     """Router, choice, weights and the experts (streamed for few tokens and on the 32-bit path, grouped tensor-core
-    products for many tokens in bf16) against the plain statement on the same rounded numbers."""
+    products for more tokens in bf16: warp-level tiles of 64 rows, and tcgen05 tiles of 128 rows from 96 pairs per
+    expert on) against the plain statement on the same rounded numbers."""
     from infero_b200.kernels import layer_ops as L, moe as M
     td = torch.float32 if dtype == "float32" else torch.bfloat16
     g = torch.Generator().manual_seed(E * 10 + top)
@@ -87,7 +92,9 @@ def test_routing_and_experts(dtype, E, top, d, ff, T):
     h, router, sg = rt(T, d), rt(E, d, k=0.5), rt(d, k=0.3)
     gate, up, down = rt(E, ff, d, k=0.3), rt(E, ff, d, k=0.3), rt(E, d, ff, k=0.3)
     shared = torch.randn(T, d, generator=g)
-    idx, w, sgate = L.moe_route(h.to(DEV), router.to(DEV), sg.to(DEV), top)
+    from infero_b200.parts.linear import Linear
+    z = Linear(torch.cat([router, sg.unsqueeze(0)]).to(DEV)).forward(h.to(DEV), out_dtype=torch.float32)
+    idx, w, sgate = L.moe_select(z, E, top, gate_col=E)
     want_idx, want_w = PV.route(h.double(), router.double(), top)
     assert torch.equal(idx.cpu().long(), want_idx)
     assert _rel(w, want_w) < 1e-5 and _rel(sgate, torch.sigmoid(h.double() @ sg.double())) < 1e-5
@@ -106,7 +113,7 @@ def test_the_lowest_index_wins_a_tie_between_experts():
     h = torch.ones(2, 8, device=DEV)
     router = torch.zeros(5, 8, device=DEV)
     router[1] = router[3] = 0.25
-    idx, w, _ = L.moe_route(h, router, None, 3)
+    idx, w, _ = L.moe_select((h @ router.T).contiguous(), 5, 3)
     assert idx.cpu().tolist() == [[1, 3, 0], [1, 3, 0]]
     e = math.exp(-2.0)
     assert torch.allclose(w.cpu(), torch.tensor([[1 / (2 + e), 1 / (2 + e), e / (2 + e)]] * 2), atol=1e-6)
@@ -125,8 +132,10 @@ class _Attn:
         self.qn, self.kn = 1 + 0.2 * torch.randn(D, generator=g), 1 + 0.2 * torch.randn(D, generator=g)
         self.base = 500.0
         self.inv = torch.tensor([self.base ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float32) if rot else None
-        self.k = torch.full((pages, G, page, 2 * D), float("nan"), dtype=self.td, device=DEV)
-        self.v = torch.full((pages, G, page, V), float("nan"), dtype=self.td, device=DEV)
+        # rows that were never written hold large numbers: a key or value read from one shows at once (finite, as
+        # whatever a used page holds is: the tiled kernels multiply masked rows by a weight of exactly 0)
+        self.k = torch.full((pages, G, page, 2 * D), 3.0e4, dtype=self.td, device=DEV)
+        self.v = torch.full((pages, G, page, V), -3.0e4, dtype=self.td, device=DEV)
         self.free = [int(p) for p in torch.randperm(pages, generator=g)]
         self.table = {}
         self.length = {}
@@ -158,17 +167,19 @@ class _Attn:
         proj = torch.cat(rows).to(DEV).contiguous()
         T = proj.shape[0]
         H, G, D, V = self.H, self.G, self.D, self.V
-        q = torch.empty(T, 2 * H * D, dtype=self.td, device=DEV)
+        padded = A.as_plain_heads(self.td, D, V, self.page)      # as the mixer decides (a value as wide as a key row)
+        q = torch.empty(T, 2 * H * D * (2 if padded else 1), dtype=self.td, device=DEV)
         dev = lambda t: None if t is None else t.to(DEV)                          # noqa: E731
         table = table.to(DEV)
         L.qkv_prepare(proj, dev(self.conv), self.taps, self.state if self.taps > 1 else None, dev(self.qn), dev(self.kn),
                       self.eps, dev(self.inv), ctx.positions, ctx.tok_entry, ctx.entry_q_start, ctx.entry_slot, table, q,
-                      self.k, self.v, self.page, 2 * H, 2 * G, G, D, V)
+                      self.k, self.v, self.page, 2 * H, 2 * G, G, D, V, q_pad=padded)
         if self.taps > 1:
             L.conv_state_update(proj, self.state, self.taps, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_slot, E, self.C)
         out = torch.empty(T, H * V, dtype=self.td, device=DEV)
         kv = types.SimpleNamespace(k=self.k, v=self.v, page_size=self.page)
-        A.paged_diff_attention(ctx, q, out, kv, table, H, G, D, V, None, self.scale, self.lam, self.eps, 1 - self.diff)
+        A.paged_diff_attention(ctx, q, out, kv, table, H, G, D, V, None, self.scale, self.lam, self.eps, 1 - self.diff,
+                               q_padded=padded)
         res = {}
         for e, (rid, _, _) in enumerate(parts):
             res[rid] = out[qs[e]:qs[e] + ql[e]].float().cpu()
@@ -200,8 +211,11 @@ class _Attn:
         return torch.cat(heads, dim=-1)
 
 
+# bf16: (32, 48) and (64, 32) take the design's own tensor-core kernel, (64, 128) and (48, 96) the engine's kernels
+# for ordinary heads (a value as wide as a key row), (24, 40) the generic kernel
 ATTN_CASES = [("float32", 2, 1, 12, 20, 4, 6), ("float32", 3, 3, 10, 14, 0, 10), ("bfloat16", 4, 2, 32, 48, 3, 16),
-              ("bfloat16", 2, 1, 64, 128, 4, 64), ("bfloat16", 2, 2, 24, 40, 2, 0)]
+              ("bfloat16", 2, 1, 64, 128, 4, 64), ("bfloat16", 2, 2, 24, 40, 2, 0), ("bfloat16", 4, 1, 48, 96, 4, 24),
+              ("bfloat16", 2, 2, 64, 32, 2, 32)]
 
 
 @pytest.mark.parametrize("dtype,H,G,D,V,taps,rot", ATTN_CASES)
