@@ -12,6 +12,8 @@ namespace {
 
 constexpr int THREADS = 256;
 
+// PER > 0: the row's d <= PER * THREADS gated values stay in registers between the two passes
+template <int PER>
 __global__ void __launch_bounds__(THREADS)
 gated_scalar_norm_add_kernel(float* __restrict__ x, const float* __restrict__ y, int y_stride,
                              const float* __restrict__ gate, int gate_stride, const float* __restrict__ gate_bias,
@@ -20,21 +22,45 @@ gated_scalar_norm_add_kernel(float* __restrict__ x, const float* __restrict__ y,
     const size_t t = blockIdx.x;
     const float* yr = y + t * y_stride;
     const float* gr = gate ? gate + t * gate_stride : nullptr;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < d; i += THREADS) {
+    auto gated = [&](int i) {
         float z = yr[i];
         if (gr) z *= 1.0f / (1.0f + expf(-(gr[i] + (gate_bias ? gate_bias[i] : 0.f))));
-        ss = fmaf(z, z, ss);
+        return z;
+    };
+    float keep[PER > 0 ? PER : 1];
+    float ss = 0.f;
+    if (PER > 0) {
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int i = k * THREADS + threadIdx.x;
+            keep[k] = i < d ? gated(i) : 0.f;
+            ss = fmaf(keep[k], keep[k], ss);
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += THREADS) {
+            const float z = gated(i);
+            ss = fmaf(z, z, ss);
+        }
     }
     ss = block_sum(ss, red);
     const float r = norm_w[0] / sqrtf(ss / (float)d + eps);
     float* xr = x + t * d;
-    for (int i = threadIdx.x; i < d; i += THREADS) {
-        float z = yr[i];
-        if (gr) z *= 1.0f / (1.0f + expf(-(gr[i] + (gate_bias ? gate_bias[i] : 0.f))));
-        const float v = xr[i] + z * r;
-        xr[i] = v;
-        if (h_out) h_out[t * d + i] = __float2bfloat16_rn(v);
+    if (PER > 0) {
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int i = k * THREADS + threadIdx.x;
+            if (i < d) {
+                const float v = xr[i] + keep[k] * r;
+                xr[i] = v;
+                if (h_out) h_out[t * d + i] = __float2bfloat16_rn(v);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += THREADS) {
+            const float v = xr[i] + gated(i) * r;
+            xr[i] = v;
+            if (h_out) h_out[t * d + i] = __float2bfloat16_rn(v);
+        }
     }
 }
 
@@ -52,8 +78,13 @@ int infero_gated_scalar_norm_add(float* x, const float* y, int y_stride, const f
                                  int n_rows, int d, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     INFERO_REQUIRE(d > 0 && y_stride >= d, "gated norm: bad sizes d=%d stride=%d", d, y_stride);
-    gated_scalar_norm_add_kernel<<<n_rows, THREADS, 0, stream>>>(x, y, y_stride, gate, gate_stride, gate_bias,
-                                                                norm_w, eps, (bf16*)h_out_bf16, d);
+#define GO(PER_) gated_scalar_norm_add_kernel<PER_><<<n_rows, THREADS, 0, stream>>>(x, y, y_stride, gate, gate_stride, gate_bias, \
+                                                                                   norm_w, eps, (bf16*)h_out_bf16, d)
+    if (d <= 4 * THREADS) GO(4);
+    else if (d <= 8 * THREADS) GO(8);
+    else if (d <= 16 * THREADS) GO(16);
+    else GO(0);
+#undef GO
     return infero_check_launch("gated_scalar_norm_add");
 }
 

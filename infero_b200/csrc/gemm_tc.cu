@@ -499,11 +499,19 @@ template <int EPI, typename OutT>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                           OutT* __restrict__ out, const void* __restrict__ bias, int bias_dtype,
-                          int RA, int RB, int K, long long ldc, int BN, int* __restrict__ err_flag,
+                          int RA_bound, int RB, int K, long long ldc, int BN, int* __restrict__ err_flag,
                           const int* __restrict__ tile_group) {
     // tile_group (or null): a grouped product.  map_b then covers several stacked [RB, K] matrices and the
     // 128-row tile m of the activations multiplies matrix tile_group[m] (a negative entry: a tile of padding
-    // rows, multiplied with matrix 0).  The table is written by a kernel in front, so it is read after the wait.
+    // rows, multiplied with matrix 0).  The entry behind the last tile's holds the number of rows in use (the
+    // launch is sized for a bound the host knows; the tiles behind the rows in use are not run).  The table is
+    // written by a kernel in front, so it is read after the wait.
+    int RA = RA_bound;
+    if (tile_group) {
+        pdl_wait();
+        const int used = tile_group[(RA_bound + TILE_A - 1) / TILE_A];
+        RA = used < RA_bound ? used : RA_bound;
+    }
     constexpr int STAGES = PERS_STAGES;
     using Plan = SmemPlan<PERS_MAX_BN, STAGES>;             // where the barriers sit; stages are packed by BN
     const int stage_bytes = A_STAGE_BYTES + BN * TILE_K * 2;

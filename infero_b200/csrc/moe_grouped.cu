@@ -54,6 +54,7 @@ __global__ void moe_align_kernel(const int* __restrict__ top_idx, int n_pairs, i
         }
         tile_expert[m] = e;
     }
+    if (threadIdx.x == 0) tile_expert[max_tiles] = total;       // rows in use (tile_expert has max_tiles + 1 entries)
     __syncthreads();
     for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
         const int e = top_idx[p];
@@ -227,7 +228,7 @@ int infero_moe_grouped_tiles(int n_pairs, int E) {
     return (n_pairs + E * (BM - 1) + BM - 1) / BM;
 }
 
-// Scratch (the caller allocates), with R = tiles * tile rows: sorted_pair, a_rows int32 [R]; tile_expert int32 [tiles];
+// Scratch (the caller allocates), with R = tiles * tile rows: sorted_pair, a_rows int32 [R]; tile_expert int32 [tiles + 1];
 // act bf16 [R, ff]; part float32 [tokens * top, d].
 int infero_moe_experts_grouped(const void* h, int h_stride, const void* gate_up, const void* down, const int* top_idx,
                                const float* top_w, const float* shared, const float* shared_gate, int* sorted_pair,
@@ -258,7 +259,7 @@ int infero_moe_experts_grouped(const void* h, int h_stride, const void* gate_up,
 // ---- the pieces around grouped products on the tcgen05 kernel (128-row tiles) ----------------------------------
 int infero_moe_tc_tiles(int n_pairs, int E) { return (n_pairs + E * 127 + 127) / 128; }
 
-// sorted_pair, a_rows int32 [tiles * 128]; tile_expert int32 [tiles]; pair_row int32 [tokens * top];
+// sorted_pair, a_rows int32 [tiles * 128]; tile_expert int32 [tiles + 1]; pair_row int32 [tokens * top];
 // xs bf16 [tiles * 128, d]: the tokens' rows in sorted order.
 int infero_moe_tc_prepare(const void* h, int h_stride, const int* top_idx, int* sorted_pair, int* a_rows, int* tile_expert,
                           int* pair_row, void* xs, int n_tokens, int d, int E, int top, cudaStream_t stream) {

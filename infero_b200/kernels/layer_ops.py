@@ -180,7 +180,7 @@ def moe_experts_grouped(h, gate_up, down, top_idx, top_w, shared, shared_gate, y
     tiles = int(lib().infero_moe_grouped_tiles(c_int(T * top), c_int(E)))
     R = tiles * int(lib().infero_moe_grouped_tile_rows(c_int(T * top), c_int(E)))
     dev = h.device
-    ints = torch.empty(2 * R + tiles, dtype=torch.int32, device=dev)
+    ints = torch.empty(2 * R + tiles + 1, dtype=torch.int32, device=dev)
     sorted_pair, a_rows, tile_expert = ints[:R], ints[R:2 * R], ints[2 * R:]
     act = torch.empty((R, ff), dtype=torch.bfloat16, device=dev)
     part = torch.empty((T * top, d), dtype=torch.float32, device=dev)
@@ -204,8 +204,8 @@ def moe_experts_tc(h, gate_up, down, top_idx, top_w, shared, shared_gate, y) -> 
     assert y.dtype == torch.float32 and y.is_contiguous() and y.shape == (T, d) and h.stride(1) == 1
     tiles = int(lib().infero_moe_tc_tiles(c_int(T * top), c_int(E)))
     R, dev = tiles * 128, h.device
-    ints = torch.empty(2 * R + tiles + T * top, dtype=torch.int32, device=dev)
-    sorted_pair, a_rows, tile_expert, pair_row = ints[:R], ints[R:2 * R], ints[2 * R:2 * R + tiles], ints[2 * R + tiles:]
+    ints = torch.empty(2 * R + tiles + 1 + T * top, dtype=torch.int32, device=dev)
+    sorted_pair, a_rows, tile_expert, pair_row = ints[:R], ints[R:2 * R], ints[2 * R:2 * R + tiles + 1], ints[2 * R + tiles + 1:]
     xs = torch.empty((R, d), dtype=torch.bfloat16, device=dev)
     _check(lib().infero_moe_tc_prepare(_ptr(h), c_int(h.stride(0)), _ptr(_i32(top_idx, "top_idx")), _ptr(sorted_pair),
                                        _ptr(a_rows), _ptr(tile_expert), _ptr(pair_row), _ptr(xs), c_int(T), c_int(d),

@@ -373,3 +373,22 @@ def test_the_trace_runner_replays_a_vufizen_folder(tmp_path):
     got = R.replay_subprocess(mdir, "float32", steps, R.max_live_tokens(steps, reqs), str(tmp_path), CONFIGS["A"]["vocab"])
     worst, where = R.compare(got, plain_logits(mdir, reqs))
     assert worst <= TOL["float32"], (worst, where)
+
+
+def test_the_generate_command_line_on_a_vufizen_folder():
+    """``bin/generate`` as a user runs it: the model is chosen by the folder's config.json."""
+    import os
+    import subprocess
+    import sys
+    mdir = model_dir("B")
+    cfg, w = plain_model(mdir)
+    prompt = make_requests("B", [21], seed=8)["r0"]
+    exe = os.path.join(R.ROOT, "bin", "generate")
+    proc = subprocess.run([sys.executable, exe, mdir] + [str(t) for t in prompt] +
+                          ["--greedy", "--repetition-penalty", "1.0", "-n", "7", "--dtype", "float32", "--ignore-eos",
+                           "--max-seq-len", "128"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr
+    lines = proc.stdout.splitlines()
+    at = next(i for i, l in enumerate(lines) if l.startswith("kv cache"))
+    toks = [int(t) for t in next(l for l in lines[at + 1:] if l.strip()).split()]
+    assert toks == _plain_greedy(cfg, w, prompt, 7)
