@@ -8,7 +8,7 @@
 //     token; what lies before this step's first token comes from the request's state slot, zeros before
 //     the sequence's start), RMS norm of every map of every query and key head with a shared weight,
 //     rotary positions on adjacent pairs (2i, 2i+1) of the first `rot` dimensions of each map, then the
-//     query to its buffer and key and value to their pages.  One block per token, 32-bit throughout.
+//     query to its buffer and key and value to their pages.  One warp per token and map, 32-bit throughout.
 // (2) conv_state_update: the last taps-1 raw product rows of every request become its new state.
 // (3) diff_attention_generic: one warp per (token, head): two causal softmaxes (32-bit, running maximum
 //     and sum, keys in ascending order in chunks of 32 aligned to absolute positions) a1, a2 over the
@@ -19,11 +19,16 @@
 
 namespace {
 
-constexpr int PREP_THREADS = 256;
+constexpr int PREP_WARPS = 8;
 constexpr int MAX_TAPS = 16;
+constexpr int SEG_MAX = 256;             // widest segment (one map of a head) a warp keeps in registers
 
+// One warp per (token, segment).  The token's channels [q | k | v] are cut into segments of D: every map of every
+// query and key head is one (normed and rotated), the values follow in pieces of D (copied).  Lane l holds channels
+// l, l + 32, ... of its segment, so loads and stores are coalesced and the partner of a rotary pair sits in the
+// neighbouring lane.
 template <typename T>
-__global__ void __launch_bounds__(PREP_THREADS)
+__global__ void __launch_bounds__(PREP_WARPS * 32)
 qkv_prepare_kernel(const float* __restrict__ proj, int stride, const float* __restrict__ conv_w, int taps,
                    const float* __restrict__ conv_state, const float* __restrict__ q_norm,
                    const float* __restrict__ k_norm, float eps, const float* __restrict__ inv_freq, int rot,
@@ -32,80 +37,104 @@ qkv_prepare_kernel(const float* __restrict__ proj, int stride, const float* __re
                    const int* __restrict__ block_table, int max_blocks, T* __restrict__ q_out, int q_stride,
                    T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int n_q_units, int n_k_units,
                    int G, int D, int V, int write_cache, int q_pad) {
-    extern __shared__ float buf[];            // this token's channels after the convolution, then rot/2 (cos, sin)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int Cq = n_q_units * D, Ck = n_k_units * D, Cv = G * V, C = Cq + Ck + Cv;
+    const int n_units = n_q_units + n_k_units, n_seg = n_units + (Cv + D - 1) / D;
+    const int seg = blockIdx.y * PREP_WARPS + warp;
     const int t = blockIdx.x;
+    const int pos = positions[t];
+    __shared__ float2 cs_tab[SEG_MAX / 2];                     // (cos, sin) of the token's angles, shared by the block's maps
+    if (blockIdx.y * PREP_WARPS < n_units) {                   // (a block of value segments only has no use for them)
+        for (int i = threadIdx.x; i < rot / 2; i += PREP_WARPS * 32) {
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            cs_tab[i] = make_float2(cs, sn);
+        }
+        __syncthreads();
+    }
+    if (seg >= n_seg) return;
     const int e = tok_entry[t];
     const int r = t - entry_q_start[e];       // index of the token among its request's new tokens
-    const int pos = positions[t];
-    const int Cq = n_q_units * D, Ck = n_k_units * D, C = Cq + Ck + G * V;
     const int keep = taps - 1;
     const float* st = (taps > 1) ? conv_state + (size_t)entry_slot[e] * keep * C : nullptr;
-    for (int c = threadIdx.x; c < C; c += PREP_THREADS) {
-        float acc;
-        if (taps <= 0) {
-            acc = proj[(size_t)t * stride + c];
-        } else {
-            acc = 0.f;
-            for (int j = 0; j < taps; ++j) {
-                const int back = keep - j;                      // how many tokens before this one
-                const float u = (r - back >= 0) ? proj[(size_t)(t - back) * stride + c]
-                                                : st[(size_t)(r - back + keep) * C + c];
-                acc = fmaf(conv_w[(size_t)c * taps + j], u, acc);
+    const int c0 = seg * D;                                   // first channel of the segment
+    const int width = seg < n_units ? D : min(D, C - c0);
+
+    float x[SEG_MAX / 32];
+#pragma unroll
+    for (int k = 0; k < SEG_MAX / 32; ++k) {
+        const int i = k * 32 + lane;
+        float acc = 0.f;
+        if (i < width) {
+            const int c = c0 + i;
+            if (taps <= 0) {
+                acc = proj[(size_t)t * stride + c];
+            } else {
+                for (int j = 0; j < taps; ++j) {
+                    const int back = keep - j;                  // how many tokens before this one
+                    const float u = (r - back >= 0) ? proj[(size_t)(t - back) * stride + c]
+                                                    : st[(size_t)(r - back + keep) * C + c];
+                    acc = fmaf(conv_w[(size_t)j * C + c], u, acc);
+                }
             }
         }
-        buf[c] = acc;
+        x[k] = acc;
     }
-    float2* cs_tab = reinterpret_cast<float2*>(buf + ((C + 1) & ~1));
-    for (int i = threadIdx.x; i < rot / 2; i += PREP_THREADS) {
-        float sn, cs;
-        sincosf((float)pos * inv_freq[i], &sn, &cs);          // once per token, shared by all heads and maps
-        cs_tab[i] = make_float2(cs, sn);
-    }
-    __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = PREP_THREADS / 32;
-    for (int u = warp; u < n_q_units + n_k_units; u += nwarps) {
-        float* x = buf + (size_t)u * D;
-        const float* w = u < n_q_units ? q_norm : k_norm;
+    if (seg < n_units) {
+        const float* w = seg < n_q_units ? q_norm : k_norm;
         if (w) {
             float ss = 0.f;
-            for (int i = lane; i < D; i += 32) ss = fmaf(x[i], x[i], ss);
+#pragma unroll
+            for (int k = 0; k < SEG_MAX / 32; ++k) ss = fmaf(x[k], x[k], ss);      // (channels beyond the width are 0)
             ss = warp_sum(ss);
             const float rn = 1.0f / sqrtf(ss / (float)D + eps);
-            for (int i = lane; i < D; i += 32) x[i] = x[i] * rn * w[i];
-            __syncwarp();
+#pragma unroll
+            for (int k = 0; k < SEG_MAX / 32; ++k) {
+                const int i = k * 32 + lane;
+                if (i < D) x[k] = x[k] * rn * w[i];
+            }
         }
-        for (int i = lane; i < rot / 2; i += 32) {
-            const float cs = cs_tab[i].x, sn = cs_tab[i].y;
-            const float a = x[2 * i], b = x[2 * i + 1];
-            x[2 * i] = a * cs - b * sn;
-            x[2 * i + 1] = b * cs + a * sn;
+#pragma unroll
+        for (int k = 0; k < SEG_MAX / 32; ++k) {
+            const int i = k * 32 + lane;                       // pair (2p, 2p + 1): the partner is the lane beside
+            const float other = __shfl_xor_sync(0xffffffffu, x[k], 1);
+            if (i < rot) {
+                const float cs = cs_tab[i >> 1].x, sn = cs_tab[i >> 1].y;
+                x[k] = (i & 1) ? x[k] * cs + other * sn : x[k] * cs - other * sn;
+            }
         }
     }
-    __syncthreads();
-    if (q_pad) {
-        // every map as a query of its own, as wide as a whole key row, with zeros where the other map's columns are:
-        // unit u = 2 head + map goes to columns [2 D u + D map, + D)
-        for (int c = threadIdx.x; c < Cq; c += PREP_THREADS) {
-            const int u = c / D, i = c - u * D, m = u & 1;
-            T* dst = q_out + (size_t)t * q_stride + (size_t)u * 2 * D;
-            dst[m * D + i] = from_f32<T>(buf[c]);
-            dst[(1 - m) * D + i] = from_f32<T>(0.f);
-        }
-    } else {
-        for (int c = threadIdx.x; c < Cq; c += PREP_THREADS) q_out[(size_t)t * q_stride + c] = from_f32<T>(buf[c]);
-    }
-    if (!write_cache) return;
-    const int page = block_table[(size_t)e * max_blocks + pos / page_size];
-    if (page < 0) return;
+    int page = -1;
     const int off = pos % page_size;
-    const int kw = Ck / G;                    // width of a key row: all maps of one kv head
-    for (int c = threadIdx.x; c < Ck; c += PREP_THREADS) {
-        const int g = c / kw, i = c - g * kw;
-        k_cache[(((size_t)page * G + g) * page_size + off) * kw + i] = from_f32<T>(buf[Cq + c]);
+    if (seg >= n_q_units) {
+        if (!write_cache) return;
+        page = block_table[(size_t)e * max_blocks + pos / page_size];
+        if (page < 0) return;
     }
-    for (int c = threadIdx.x; c < G * V; c += PREP_THREADS) {
-        const int g = c / V, i = c - g * V;
-        v_cache[(((size_t)page * G + g) * page_size + off) * V + i] = from_f32<T>(buf[Cq + Ck + c]);
+    const int kw = G > 0 ? Ck / G : 0;                         // width of a key row: all maps of one kv head
+#pragma unroll
+    for (int k = 0; k < SEG_MAX / 32; ++k) {
+        const int i = k * 32 + lane;
+        if (i >= width) continue;
+        const int c = c0 + i;
+        if (seg < n_q_units) {
+            if (q_pad) {
+                // every map as a query of its own, as wide as a whole key row, with zeros where the other map's
+                // columns are: unit u = 2 head + map goes to columns [2 D u + D map, + D)
+                const int m = seg & 1;
+                T* dst = q_out + (size_t)t * q_stride + (size_t)seg * 2 * D;
+                dst[m * D + i] = from_f32<T>(x[k]);
+                dst[(1 - m) * D + i] = from_f32<T>(0.f);
+            } else {
+                q_out[(size_t)t * q_stride + c] = from_f32<T>(x[k]);
+            }
+        } else if (seg < n_units) {
+            const int ck = c - Cq, g = ck / kw, ii = ck - g * kw;
+            k_cache[(((size_t)page * G + g) * page_size + off) * kw + ii] = from_f32<T>(x[k]);
+        } else {
+            const int cv = c - Cq - Ck, g = cv / V, ii = cv - g * V;
+            v_cache[(((size_t)page * G + g) * page_size + off) * V + ii] = from_f32<T>(x[k]);
+        }
     }
 }
 
@@ -269,7 +298,8 @@ int infero_diff_combine(const void* maps, int maps_stride, void* out, int out_st
 
 
 // proj float32 [tokens, stride]: columns [q (n_q_units*D) | k (n_k_units*D) | v (G*V)] in front.
-// conv_w float32 [C, taps] for those C channels in that order; conv_state float32 [slots, taps-1, C].
+// conv_w float32 [taps, C] (tap j of channel c at j * C + c; the channels in that order); conv_state float32
+// [slots, taps-1, C].
 // taps 0: no convolution.  q_norm / k_norm float32 [D] or null.  inv_freq float32 [rot/2] (rot 0: none).
 int infero_qkv_prepare(const float* proj, int stride, const float* conv_w, int taps, const float* conv_state,
                        const float* q_norm, const float* k_norm, float eps, const float* inv_freq, int rot,
@@ -280,22 +310,18 @@ int infero_qkv_prepare(const float* proj, int stride, const float* conv_w, int t
     if (n_tokens == 0) return 0;
     INFERO_REQUIRE(taps <= MAX_TAPS, "qkv_prepare: %d taps, at most %d", taps, MAX_TAPS);
     INFERO_REQUIRE(G > 0 && n_k_units % G == 0 && rot % 2 == 0 && rot <= D, "qkv_prepare: bad sizes");
-    const int C = (n_q_units + n_k_units) * D + G * V;
-    const size_t smem = (size_t)(((C + 1) & ~1) + rot) * sizeof(float);
-    INFERO_REQUIRE(smem <= 200 * 1024, "qkv_prepare: %d channels do not fit shared memory", C);
-    if (dtype == INFERO_F32) {
-        auto kern = qkv_prepare_kernel<float>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kern<<<n_tokens, PREP_THREADS, smem, stream>>>(proj, stride, conv_w, taps, conv_state, q_norm, k_norm, eps,
-            inv_freq, rot, positions, tok_entry, entry_q_start, entry_slot, block_table, max_blocks, (float*)q_out,
+    INFERO_REQUIRE(D >= 1 && D <= SEG_MAX, "qkv_prepare: map width %d outside 1..%d", D, SEG_MAX);
+    const int n_seg = n_q_units + n_k_units + (G * V + D - 1) / D;
+    INFERO_REQUIRE(n_seg <= 65535 * PREP_WARPS, "qkv_prepare: %d maps are too many", n_seg);
+    const dim3 grid(n_tokens, (n_seg + PREP_WARPS - 1) / PREP_WARPS);
+    if (dtype == INFERO_F32)
+        qkv_prepare_kernel<float><<<grid, PREP_WARPS * 32, 0, stream>>>(proj, stride, conv_w, taps, conv_state, q_norm, k_norm,
+            eps, inv_freq, rot, positions, tok_entry, entry_q_start, entry_slot, block_table, max_blocks, (float*)q_out,
             q_stride, (float*)k_cache, (float*)v_cache, page_size, n_q_units, n_k_units, G, D, V, write_cache, q_pad);
-    } else {
-        auto kern = qkv_prepare_kernel<bf16>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kern<<<n_tokens, PREP_THREADS, smem, stream>>>(proj, stride, conv_w, taps, conv_state, q_norm, k_norm, eps,
-            inv_freq, rot, positions, tok_entry, entry_q_start, entry_slot, block_table, max_blocks, (bf16*)q_out,
+    else
+        qkv_prepare_kernel<bf16><<<grid, PREP_WARPS * 32, 0, stream>>>(proj, stride, conv_w, taps, conv_state, q_norm, k_norm,
+            eps, inv_freq, rot, positions, tok_entry, entry_q_start, entry_slot, block_table, max_blocks, (bf16*)q_out,
             q_stride, (bf16*)k_cache, (bf16*)v_cache, page_size, n_q_units, n_k_units, G, D, V, write_cache, q_pad);
-    }
     return infero_check_launch("qkv_prepare");
 }
 

@@ -25,23 +25,24 @@ constexpr int CHUNK = 128, LONG = 512;
 enum { WHOLE = 0, LOCAL = 1, FROM_START = 2 };
 
 template <typename T, int DPT>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(512, DPT <= 16 ? 2 : 1)
 hgrn2_scan_kernel(const float* __restrict__ proj, int stride, int q_off, int f_off, int v_off,
                   const float* __restrict__ f_bias, const float* __restrict__ lower,
                   const float* __restrict__ out_w, float eps, float* __restrict__ state,
                   const int* __restrict__ entry_q_start, const int* __restrict__ entry_q_len,
                   const int* __restrict__ entry_slot, T* __restrict__ out, int out_stride,
                   int H, int D, int V, int DS, int mode, float* __restrict__ chunk_state, float* __restrict__ chunk_decay,
-                  const int* __restrict__ entry_chunk0) {
-    extern __shared__ float sm[];
+                  const int* __restrict__ entry_chunk0, int long_from) {
+    extern __shared__ __align__(16) float sm[];
     float* qs = sm;                      // [TT][D]
     float* fs = qs + TT * D;             // [TT][D]
-    float* vs = fs + TT * D;             // [TT][V]
+    float* gs = fs + TT * D;             // [TT][D]: 1 - f
+    float* vs = gs + TT * D;             // [TT][V]
     float* part = vs + TT * V;           // [TT][DS][V]
     const int h = blockIdx.x, e = blockIdx.y;
     int row0 = entry_q_start[e], n = entry_q_len[e];
     const int slot = entry_slot[e];
-    const bool is_long = n >= LONG;
+    const bool is_long = n >= long_from;                    // (without scratch for chunks every portion runs whole)
     if ((mode == WHOLE) == is_long) return;                 // long portions go by chunks, the others whole
     float* st_chunk = nullptr;
     float* decay = nullptr;
@@ -75,7 +76,9 @@ hgrn2_scan_kernel(const float* __restrict__ proj, int stride, int q_off, int f_o
             qs[tt * D + i] = qv / (1.0f + expf(-qv));
             const float fr = pr[f_off + h * D + i] + f_bias[h * D + i];
             const float l = lower[h * D + i];
-            fs[tt * D + i] = l + (1.0f - l) * (1.0f / (1.0f + expf(-fr)));
+            const float f = l + (1.0f - l) * (1.0f / (1.0f + expf(-fr)));
+            fs[tt * D + i] = f;
+            gs[tt * D + i] = 1.0f - f;
         }
         for (int idx = tid; idx < nt * V; idx += nthreads) {
             const int tt = idx / V, jj = idx - tt * V;
@@ -83,20 +86,41 @@ hgrn2_scan_kernel(const float* __restrict__ proj, int stride, int q_off, int f_o
         }
         __syncthreads();
         if (active) {
-            for (int tt = 0; tt < nt; ++tt) {
+            const bool vec = (D & 3) == 0 && i0 + DPT <= D;      // this thread's channels as 16-byte reads (all lanes alike)
+            // one token: S <- f S + g v_j (g = 1 - f), and, unless only the end state is wanted, o_j += S q
+            auto token = [&](int tt) {
                 const float vj = vs[tt * V + j];
                 float o = 0.f;
+                if (vec) {
+                    const float4* f4 = reinterpret_cast<const float4*>(fs + tt * D + i0);
+                    const float4* g4 = reinterpret_cast<const float4*>(gs + tt * D + i0);
+                    const float4* q4 = reinterpret_cast<const float4*>(qs + tt * D + i0);
 #pragma unroll
-                for (int ii = 0; ii < DPT; ++ii) {
-                    if (i0 + ii < D) {
-                        const float f = fs[tt * D + i0 + ii];
-                        S[ii] = fmaf(f, S[ii], (1.0f - f) * vj);
-                        o = fmaf(S[ii], qs[tt * D + i0 + ii], o);
-
+                    for (int k = 0; k < DPT / 4; ++k) {
+                        const float4 f = f4[k], g = g4[k];
+                        S[4 * k] = fmaf(f.x, S[4 * k], g.x * vj);
+                        S[4 * k + 1] = fmaf(f.y, S[4 * k + 1], g.y * vj);
+                        S[4 * k + 2] = fmaf(f.z, S[4 * k + 2], g.z * vj);
+                        S[4 * k + 3] = fmaf(f.w, S[4 * k + 3], g.w * vj);
+                        if (mode != LOCAL) {
+                            const float4 q = q4[k];
+                            o = fmaf(S[4 * k], q.x, o), o = fmaf(S[4 * k + 1], q.y, o);
+                            o = fmaf(S[4 * k + 2], q.z, o), o = fmaf(S[4 * k + 3], q.w, o);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int ii = 0; ii < DPT; ++ii) {
+                        if (i0 + ii < D) {
+                            S[ii] = fmaf(fs[tt * D + i0 + ii], S[ii], gs[tt * D + i0 + ii] * vj);
+                            o = fmaf(S[ii], qs[tt * D + i0 + ii], o);
+                        }
                     }
                 }
-                part[(tt * DS + s) * V + j] = o;
-            }
+                if (mode != LOCAL) part[(tt * DS + s) * V + j] = o;
+            };
+#pragma unroll 1
+            for (int tt = 0; tt < nt; ++tt) token(tt);
         }
         if (mode == LOCAL) {                                 // (channel i stays with the same thread in every round)
             for (int i = tid; i < D; i += nthreads) {
@@ -133,7 +157,8 @@ hgrn2_scan_kernel(const float* __restrict__ proj, int stride, int q_off, int f_o
     }
 }
 
-// S_(c+1) = diag(P_c) S_c + L_c over the chunks of every long portion; chunk_state[c] becomes S_c.
+// S_(c+1) = diag(P_c) S_c + L_c over the chunks of every long portion; chunk_state[c] becomes S_c.  One thread per
+// element of the state; the chunks' values are fetched eight at a time before the chain runs over them.
 __global__ void hgrn2_chain_kernel(float* __restrict__ state, float* __restrict__ chunk_state,
                                    const float* __restrict__ chunk_decay, const int* __restrict__ entry_q_len,
                                    const int* __restrict__ entry_slot, const int* __restrict__ entry_chunk0,
@@ -141,20 +166,31 @@ __global__ void hgrn2_chain_kernel(float* __restrict__ state, float* __restrict_
     const int h = blockIdx.x, e = blockIdx.y;
     const int n = entry_q_len[e];
     if (n < LONG) return;
+    const int idx = blockIdx.z * blockDim.x + threadIdx.x;
+    if (idx >= D * V) return;
     const int chunks = (n + CHUNK - 1) / CHUNK;
+    const int i = idx / V;
     float* st = state + (((size_t)entry_slot[e] * H + h) * D) * V;
-    for (int idx = threadIdx.x; idx < D * V; idx += blockDim.x) {
-        const int i = idx / V;
-        float S = st[idx];
-        for (int c = 0; c < chunks; ++c) {
-            const size_t ci = (size_t)entry_chunk0[e] + c;
-            float* L = chunk_state + (ci * H + h) * D * V;
-            const float l = L[idx];
-            L[idx] = S;
-            S = fmaf(chunk_decay[(ci * H + h) * D + i], S, l);
+    float S = st[idx];
+    const size_t c_first = (size_t)entry_chunk0[e];
+    for (int c0 = 0; c0 < chunks; c0 += 8) {
+        float l[8], p[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (c0 + k < chunks) {
+                l[k] = chunk_state[((c_first + c0 + k) * H + h) * D * V + idx];
+                p[k] = chunk_decay[((c_first + c0 + k) * H + h) * D + i];
+            }
         }
-        st[idx] = S;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (c0 + k < chunks) {
+                chunk_state[((c_first + c0 + k) * H + h) * D * V + idx] = S;
+                S = fmaf(p[k], S, l[k]);
+            }
+        }
     }
+    st[idx] = S;
 }
 
 template <typename T, int DPT>
@@ -164,7 +200,7 @@ int launch(const float* proj, int stride, int q_off, int f_off, int v_off, const
            const int* entry_chunk0, int any_short, cudaStream_t stream) {
     const int DS = (D + DPT - 1) / DPT;
     const int threads = ((V * DS + 31) / 32) * 32;
-    const size_t smem = ((size_t)TT * (2 * D + V + DS * V) + D) * sizeof(float);
+    const size_t smem = ((size_t)TT * (3 * D + V + DS * V) + D) * sizeof(float);
     auto kern = hgrn2_scan_kernel<T, DPT>;
     if (smem > 48 * 1024) {
         INFERO_REQUIRE(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess,
@@ -172,13 +208,14 @@ int launch(const float* proj, int stride, int q_off, int f_off, int v_off, const
     }
     if (any_short)
         kern<<<dim3(H, E), threads, smem, stream>>>(proj, stride, q_off, f_off, v_off, f_bias, lower, out_w, eps, state,
-                                                    qs, ql, es, (T*)out, out_stride, H, D, V, DS, WHOLE, nullptr, nullptr, nullptr);
+                                                    qs, ql, es, (T*)out, out_stride, H, D, V, DS, WHOLE, nullptr, nullptr, nullptr,
+                                                    max_chunks > 0 ? LONG : 0x7fffffff);
     if (max_chunks > 0) {
         kern<<<dim3(H, E, max_chunks), threads, smem, stream>>>(proj, stride, q_off, f_off, v_off, f_bias, lower, out_w, eps,
-            state, qs, ql, es, (T*)out, out_stride, H, D, V, DS, LOCAL, chunk_state, chunk_decay, entry_chunk0);
-        hgrn2_chain_kernel<<<dim3(H, E), 256, 0, stream>>>(state, chunk_state, chunk_decay, ql, es, entry_chunk0, H, D, V);
+            state, qs, ql, es, (T*)out, out_stride, H, D, V, DS, LOCAL, chunk_state, chunk_decay, entry_chunk0, LONG);
+        hgrn2_chain_kernel<<<dim3(H, E, (D * V + 255) / 256), 256, 0, stream>>>(state, chunk_state, chunk_decay, ql, es, entry_chunk0, H, D, V);
         kern<<<dim3(H, E, max_chunks), threads, smem, stream>>>(proj, stride, q_off, f_off, v_off, f_bias, lower, out_w, eps,
-            state, qs, ql, es, (T*)out, out_stride, H, D, V, DS, FROM_START, chunk_state, chunk_decay, entry_chunk0);
+            state, qs, ql, es, (T*)out, out_stride, H, D, V, DS, FROM_START, chunk_state, chunk_decay, entry_chunk0, LONG);
     }
     return infero_check_launch("hgrn2_scan");
 }

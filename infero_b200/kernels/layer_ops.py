@@ -60,7 +60,9 @@ def hgrn2_scan(proj: torch.Tensor, q_off: int, f_off: int, v_off: int, f_bias: t
             for c in counts:
                 firsts.append(total)
                 total += c
-            chunk0 = torch.tensor(firsts, dtype=torch.int32).to(proj.device, non_blocking=True)
+            host = torch.empty(len(firsts), dtype=torch.int32, pin_memory=True)     # (pinned: the copy is asynchronous)
+            host.numpy()[:] = firsts
+            chunk0 = host.to(proj.device, non_blocking=True)
             chunk_state = torch.empty((total, H, D, V), dtype=torch.float32, device=proj.device)
             chunk_decay = torch.empty((total, H, D), dtype=torch.float32, device=proj.device)
     _check(lib().infero_hgrn2_scan(_ptr(proj), c_int(proj.stride(0)), c_int(q_off), c_int(f_off), c_int(v_off),
@@ -85,8 +87,8 @@ def qkv_prepare(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int, c
                 inv_freq: Optional[torch.Tensor], positions, tok_entry, entry_q_start, entry_slot, block_table,
                 q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int, n_q_units: int,
                 n_k_units: int, G: int, D: int, V: int, write_cache: bool = True, q_pad: bool = False) -> None:
-    """Convolution over time, per-map RMS norm, adjacent-pair rotary, q to ``q_out``, k and v to their pages;
-    see csrc/diff_attention.cu.  ``q_pad``: q_out is [T, n_q_units * 2 D], every map a query as wide as a key row
+    """Convolution over time (``conv_w`` float32 [taps, channels]), per-map RMS norm, adjacent-pair rotary, q to
+    ``q_out``, k and v to their pages; see csrc/diff_attention.cu.  ``q_pad``: q_out is [T, n_q_units * 2 D], every map a query as wide as a key row
     with zeros in the other map's columns."""
     T = q_out.shape[0]
     assert q_out.shape[1] == n_q_units * D * (2 if q_pad else 1)
@@ -94,6 +96,7 @@ def qkv_prepare(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int, c
     assert k_cache.dtype == q_out.dtype == v_cache.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert k_cache.shape[-1] == (n_k_units // G) * D and v_cache.shape[-1] == V and k_cache.shape[1] == G
     _f32(conv_w, "conv_w"), _f32(conv_state, "conv_state"), _f32(q_norm, "q_norm"), _f32(k_norm, "k_norm")
+    assert conv_w is None or tuple(conv_w.shape) == (taps, (n_q_units + n_k_units) * D + G * V)
     rot = 0 if inv_freq is None else 2 * inv_freq.numel()
     _check(lib().infero_qkv_prepare(
         _ptr(proj), c_int(proj.stride(0)), _ptr(conv_w), c_int(taps), _ptr(conv_state), _ptr(q_norm), _ptr(k_norm),

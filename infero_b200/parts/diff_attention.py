@@ -76,7 +76,8 @@ class DiffAttention(Mixer):
         f32 = lambda r: tensors[self._n(r, False)].float().contiguous()          # noqa: E731
         self.q_norm = f32("q_norm") if s.qk_norm else None
         self.k_norm = f32("k_norm") if s.qk_norm else None
-        self.conv_w = torch.cat([f32("q_conv"), f32("k_conv"), f32("v_conv")], dim=0).contiguous() if self.taps > 0 else None
+        # stored [channels, taps]; the kernel reads tap j of all channels side by side
+        self.conv_w = torch.cat([f32("q_conv"), f32("k_conv"), f32("v_conv")], dim=0).t().contiguous() if self.taps > 0 else None
         v = {r: tensors[self._n(r, False)].double().cpu() for r in ("lq1", "lk1", "lq2", "lk2")}
         self.lam = math.exp(float((v["lq1"] * v["lk1"]).sum())) - math.exp(float((v["lq2"] * v["lk2"]).sum())) + s.diff
 

@@ -207,7 +207,7 @@ def time_kernels(z, T, context, batch, timer, peaks):
         fb, lo, wn = rnd(H * D, dtype=torch.float32), torch.rand(H * D, device=dev), torch.ones(V, device=dev)
         out = torch.empty(n, H * V, dtype=bf, device=dev)
         ms = timer(lambda: L.hgrn2_scan(proj, 0, H * D, 2 * H * D, fb, lo, wn, 1e-5, state, ctx.entry_q_start, ctx.entry_q_len,
-                                        ctx.entry_slot, out, len(q_lens), H, D, V))
+                                        ctx.entry_slot, out, len(q_lens), H, D, V, q_lens=q_lens))
         note(f"hgrn2_scan_{label}", ms, 4.0 * n * (2 * H * D + H * V) + 2.0 * n * H * V + 8.0 * len(q_lens) * H * D * V)
 
     # ---- feed-forward: routed experts beside a dense SwiGLU of the width one token uses -----------------------------
@@ -245,7 +245,7 @@ def time_kernels(z, T, context, batch, timer, peaks):
     note("add_rmsnorm_prefill", ms, T * d * (4 + 4 + 4 + 2))
     ctx, table, pages = batch_ctx([T], [0])
     C = 2 * H * D + 2 * G * D + G * V
-    proj, cw = rnd(T, C, dtype=torch.float32), rnd(C, 4, dtype=torch.float32)
+    proj, cw = rnd(T, C, dtype=torch.float32), rnd(4, C, dtype=torch.float32)
     st = torch.zeros(1, 3, C, device=dev)
     kd, vd = torch.empty(pages, G, 16, 2 * D, dtype=bf, device=dev), torch.empty(pages, G, 16, V, dtype=bf, device=dev)
     qn, inv = torch.ones(D, device=dev), torch.rand(D // 2, device=dev)

@@ -171,7 +171,7 @@ class _Attn:
         q = torch.empty(T, 2 * H * D * (2 if padded else 1), dtype=self.td, device=DEV)
         dev = lambda t: None if t is None else t.to(DEV)                          # noqa: E731
         table = table.to(DEV)
-        L.qkv_prepare(proj, dev(self.conv), self.taps, self.state if self.taps > 1 else None, dev(self.qn), dev(self.kn),
+        L.qkv_prepare(proj, dev(None if self.conv is None else self.conv.t().contiguous()), self.taps, self.state if self.taps > 1 else None, dev(self.qn), dev(self.kn),
                       self.eps, dev(self.inv), ctx.positions, ctx.tok_entry, ctx.entry_q_start, ctx.entry_slot, table, q,
                       self.k, self.v, self.page, 2 * H, 2 * G, G, D, V, q_pad=padded)
         if self.taps > 1:
