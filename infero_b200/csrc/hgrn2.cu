@@ -25,7 +25,7 @@ constexpr int CHUNK = 128, LONG = 512;
 enum { WHOLE = 0, LOCAL = 1, FROM_START = 2 };
 
 template <typename T, int DPT>
-__global__ void __launch_bounds__(512, DPT <= 16 ? 2 : 1)
+__global__ void __launch_bounds__(512, DPT <= 16 ? 2 : 1)          // (64 rows per thread: wide states, slow but whole)
 hgrn2_scan_kernel(const float* __restrict__ proj, int stride, int q_off, int f_off, int v_off,
                   const float* __restrict__ f_bias, const float* __restrict__ lower,
                   const float* __restrict__ out_w, float eps, float* __restrict__ state,
@@ -240,15 +240,15 @@ int infero_hgrn2_scan(const float* proj, int stride, int q_off, int f_off, int v
     if (n_entries == 0) return 0;
     INFERO_REQUIRE(H > 0 && D > 0 && V > 0 && V <= 512, "hgrn2: bad sizes H=%d D=%d V=%d", H, D, V);
     int dpt = 8;
-    while (dpt < 32 && V * ((D + dpt - 1) / dpt) > 512) dpt *= 2;
+    while (dpt < 64 && V * ((D + dpt - 1) / dpt) > 512) dpt *= 2;
     INFERO_REQUIRE(V * ((D + dpt - 1) / dpt) <= 512, "hgrn2: a state of %d x %d per head is too large", D, V);
 #define GO(TY, N) return launch<TY, N>(proj, stride, q_off, f_off, v_off, f_bias, lower, out_w, eps, state, \
                                        entry_q_start, entry_q_len, entry_slot, out, out_stride, n_entries, H, D, V, max_chunks, chunk_state, \
                                        chunk_decay, entry_chunk0, any_short, stream)
     if (out_dtype == INFERO_F32) {
-        if (dpt == 8) GO(float, 8); if (dpt == 16) GO(float, 16); GO(float, 32);
+        if (dpt == 8) GO(float, 8); if (dpt == 16) GO(float, 16); if (dpt == 32) GO(float, 32); GO(float, 64);
     } else {
-        if (dpt == 8) GO(bf16, 8); if (dpt == 16) GO(bf16, 16); GO(bf16, 32);
+        if (dpt == 8) GO(bf16, 8); if (dpt == 16) GO(bf16, 16); if (dpt == 32) GO(bf16, 32); GO(bf16, 64);
     }
 #undef GO
 }

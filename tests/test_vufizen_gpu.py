@@ -40,9 +40,9 @@ def test_gated_norm_add_kernel():
     assert _rel(xd, x.double() + 1.3 * PV.unit_rms(y.double(), 1e-5)) < 2e-6
 
 
-@pytest.mark.parametrize("H,D,V,lens", [(2, 16, 32, [9, 1, 20]), (1, 12, 20, [9, 1, 20]), (3, 48, 64, [9, 1, 20]),
+@pytest.mark.parametrize("H,D,V,lens", [(2, 16, 32, [9, 1, 20]), (1, 12, 20, [9, 1, 20]), (3, 40, 72, [9, 1, 20]),
                                         (2, 128, 128, [9, 1, 20]), (1, 200, 40, [9, 1, 20]),
-                                        (2, 16, 32, [515, 1, 260]), (1, 48, 64, [130, 700, 512])])
+                                        (2, 16, 32, [515, 1, 260]), (1, 40, 72, [130, 700, 512])])
 def test_hgrn2_scan_kernel(H, D, V, lens):
     """Three requests of unequal length in one launch, then continued from their state slots in a second one
     in another order; slots are not the entries' indices.  Portions of 512 tokens and more run by chunks side by
@@ -211,10 +211,10 @@ class _Attn:
         return torch.cat(heads, dim=-1)
 
 
-# bf16: (32, 48) and (64, 32) take the design's own tensor-core kernel, (64, 128) and (48, 96) the engine's kernels
+# bf16: (32, 48) and (64, 32) take the design's own tensor-core kernel, (64, 128) and (40, 80) the engine's kernels
 # for ordinary heads (a value as wide as a key row), (24, 40) the generic kernel
 ATTN_CASES = [("float32", 2, 1, 12, 20, 4, 6), ("float32", 3, 3, 10, 14, 0, 10), ("bfloat16", 4, 2, 32, 48, 3, 16),
-              ("bfloat16", 2, 1, 64, 128, 4, 64), ("bfloat16", 2, 2, 24, 40, 2, 0), ("bfloat16", 4, 1, 48, 96, 4, 24),
+              ("bfloat16", 2, 1, 64, 128, 4, 64), ("bfloat16", 2, 2, 24, 40, 2, 0), ("bfloat16", 6, 3, 40, 80, 2, 20),
               ("bfloat16", 2, 2, 64, 32, 2, 32)]
 
 
@@ -281,7 +281,8 @@ def test_a_far_key_is_found(dtype, far):
 
 
 # ---- whole models through the step function ---------------------------------------------------------------------
-def _replay(name, dtype, steps_of, lengths, seed=0, page_size=16, max_seqs=3, tol=None):
+def _replay(name, dtype, steps_of, lengths, seed=0, page_size=16, max_seqs=3, tol=None, spread=None):
+    """``spread`` = (median, 90th percentile): bound the distribution of the rows' errors instead of their maximum."""
     mdir = model_dir(name)
     reqs = make_requests(name, lengths, seed=seed)
     plain = plain_logits(mdir, reqs)
@@ -289,8 +290,13 @@ def _replay(name, dtype, steps_of, lengths, seed=0, page_size=16, max_seqs=3, to
     runner = make_runner(mdir, dtype, R.max_live_tokens(steps, reqs), page_size=page_size, max_seqs=max_seqs)
     got = R.replay_inprocess(runner, steps)
     assert len(got) > 0
-    worst, where = R.compare(got, plain)
-    assert worst <= (tol or TOL[dtype]), f"{name} {dtype}: {worst:.3e} at {where}"
+    if spread is not None:
+        errs = np.array([np.abs(row.astype(np.float64) - plain[rid][p]).max() / np.abs(plain[rid]).max() for (rid, p), row in got.items()])
+        assert np.isfinite(errs).all() and np.median(errs) <= spread[0] and np.quantile(errs, 0.9) <= spread[1], \
+            f"{name} {dtype}: median {np.median(errs):.3e}, 90 % below {np.quantile(errs, 0.9):.3e}"
+    else:
+        worst, where = R.compare(got, plain)
+        assert worst <= (tol or TOL[dtype]), f"{name} {dtype}: {worst:.3e} at {where}"
     assert not runner.manager.requests
     return runner
 
@@ -335,6 +341,25 @@ def test_a_batch_equals_each_request_alone_bitwise_in_32_bit():
 def test_three_hundred_single_tokens():
     _replay("B", "float32", lambda r: R.steps_tail_decode(r, tail=300), [310])
     _replay("D", "bfloat16", lambda r: R.steps_tail_decode(r, tail=300), [305])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_no_fast_kernel_takes(dtype):
+    """A width of 36, prime head sizes, one tap: every product and kernel on its any-shape path, in both precisions.
+    (Norms over 6 to 10 values pass more of a 32-bit rounding on than norms over 32 and more: the worst row of the
+    32-bit run is at 4e-5 here, where the other configurations stay below 1e-5.  In bf16 a head of ten values whose two
+    maps nearly cancel, or a recurrent head of seven, blows a rounding up at a few positions (worst rows at 0.2, whatever
+    the cut), so the bf16 run bounds the median and the ninth decile of the rows' errors: measured 0.02 and 0.07.)"""
+    tol = 1e-4 if dtype == "float32" else None
+    spread = (0.04, 0.12) if dtype == "bfloat16" else None
+    _replay("E", dtype, lambda r: R.steps_mixed(r, seed=7, max_live=3), [70, 33, 18, 41], tol=tol, spread=spread)
+    _replay("E", dtype, lambda r: R.steps_tail_decode(r, tail=20), [45], tol=tol, spread=spread)
+
+
+def test_a_wide_recurrent_state():
+    """128 x 256 per head: sixty-four rows of the state per thread."""
+    test_hgrn2_scan_kernel(1, 128, 256, [9, 1, 20])
+    test_hgrn2_scan_kernel(1, 100, 256, [515, 3, 20])
 
 
 def test_page_size_64():

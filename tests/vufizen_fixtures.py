@@ -73,7 +73,16 @@ D = _copy.deepcopy(A)
 for _l in D["layers"]:
     if _l["mlp"]:
         _l["mlp"]["router"]["top"] = _l["mlp"]["router"]["experts"]
-CONFIGS = {"A": A, "B": B, "C": C, "D": D}
+# E: a width that is no multiple of 8 (no tensor-core product takes it), prime sizes, one tap, one rotated pair, a
+#    shared expert only where top = experts, kv_heads and scale left to their defaults
+E = {"architecture": "Vufizen", "vocab": 53, "width": 36, "norm": {"eps": 3e-6}, "layers": [
+    {"type": "attention", "mixer": {"heads": 3, "dim": 6, "vdim": 10, "conv": 1, "diff": 0.45, "rot": {"base": 77.0, "dims": 2}},
+     "mlp": _moe(7, 7, 10, shared=6)},
+    {"type": "hgrn2", "mixer": {"heads": 3, "dim": 5, "vdim": 7}, "mlp": _moe(7, 7, 10, shared=6)},
+    {"type": "attention", "mixer": {"heads": 3, "dim": 6, "vdim": 10, "conv": 1, "diff": 0.45, "rot": {"base": 77.0, "dims": 2}},
+     "mlp": _moe(7, 7, 10, shared=6), "weights_of": 0},
+]}
+CONFIGS = {"A": A, "B": B, "C": C, "D": D, "E": E}
 
 
 @functools.lru_cache(maxsize=None)
