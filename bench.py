@@ -282,7 +282,7 @@ def main(argv=None) -> int:
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
-                    help="size of the timed prompt step (the contract's 2,048; 8,192 and more show attention over long contexts)")
+                    help="size of the timed prompt step (2,048 by default; 8,192 and more show attention over long contexts)")
     ap.add_argument("--designs", action="store_true",
                     help="instead of the headline workload: Vufizen beside Qwen2 at equal layer sizes, prompt and decode "
                          "steps and the kernels alone (infero_b200/tools/design_bench.py; its own JSON line)")

@@ -21,7 +21,7 @@ from .step import ModelRunner, StepEntry
 def _auto_pages(model, page_size: int, act_dtype, device, max_seqs: int, ctx: int,
                 fraction: Optional[float], max_batch_tokens: int) -> int:
     """Pages (of the groups that keep every key) that fit beside the weights: the reference leaves 1/8
-    of the card plus 512 MiB free (crates/server/src/scheduler.rs:2341-2432); never more than max_seqs
+    of the GPU's memory plus 512 MiB free (crates/server/src/scheduler.rs:2341-2432); never more than max_seqs
     full contexts.  A group that keeps a window has a pool of fixed size, which comes off the room first."""
     from ..cache.storage import window_pool_pages
     esize = 2 if act_dtype == torch.bfloat16 else 4
