@@ -24,15 +24,16 @@ constexpr int TT = 8;      // tokens staged per round
 constexpr int CHUNK = 128, LONG = 512;
 enum { WHOLE = 0, LOCAL = 1, FROM_START = 2 };
 
-template <typename T, int DPT>
+template <typename T, int DPT, int MODE>
 __global__ void __launch_bounds__(512, DPT <= 16 ? 2 : 1)          // (64 rows per thread: wide states, slow but whole)
 hgrn2_scan_kernel(const float* __restrict__ proj, int stride, int q_off, int f_off, int v_off,
                   const float* __restrict__ f_bias, const float* __restrict__ lower,
                   const float* __restrict__ out_w, float eps, float* __restrict__ state,
                   const int* __restrict__ entry_q_start, const int* __restrict__ entry_q_len,
                   const int* __restrict__ entry_slot, T* __restrict__ out, int out_stride,
-                  int H, int D, int V, int DS, int mode, float* __restrict__ chunk_state, float* __restrict__ chunk_decay,
+                  int H, int D, int V, int DS, float* __restrict__ chunk_state, float* __restrict__ chunk_decay,
                   const int* __restrict__ entry_chunk0, int long_from) {
+    constexpr int mode = MODE;
     extern __shared__ __align__(16) float sm[];
     float* qs = sm;                      // [TT][D]
     float* fs = qs + TT * D;             // [TT][D]
@@ -72,8 +73,10 @@ hgrn2_scan_kernel(const float* __restrict__ proj, int stride, int q_off, int f_o
         for (int idx = tid; idx < nt * D; idx += nthreads) {
             const int tt = idx / D, i = idx - tt * D;
             const float* pr = proj + (size_t)(row0 + t0 + tt) * stride;
-            const float qv = pr[q_off + h * D + i];
-            qs[tt * D + i] = qv / (1.0f + expf(-qv));
+            if (mode != LOCAL) {
+                const float qv = pr[q_off + h * D + i];
+                qs[tt * D + i] = qv / (1.0f + expf(-qv));
+            }
             const float fr = pr[f_off + h * D + i] + f_bias[h * D + i];
             const float l = lower[h * D + i];
             const float f = l + (1.0f - l) * (1.0f / (1.0f + expf(-fr)));
@@ -201,21 +204,25 @@ int launch(const float* proj, int stride, int q_off, int f_off, int v_off, const
     const int DS = (D + DPT - 1) / DPT;
     const int threads = ((V * DS + 31) / 32) * 32;
     const size_t smem = ((size_t)TT * (3 * D + V + DS * V) + D) * sizeof(float);
-    auto kern = hgrn2_scan_kernel<T, DPT>;
+    auto kern = hgrn2_scan_kernel<T, DPT, WHOLE>;
+    auto kern_local = hgrn2_scan_kernel<T, DPT, LOCAL>;
+    auto kern_from = hgrn2_scan_kernel<T, DPT, FROM_START>;
     if (smem > 48 * 1024) {
-        INFERO_REQUIRE(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess,
+        INFERO_REQUIRE(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess &&
+                       cudaFuncSetAttribute(kern_local, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess &&
+                       cudaFuncSetAttribute(kern_from, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess,
                        "hgrn2: %zu bytes of shared memory are not available", smem);
     }
     if (any_short)
         kern<<<dim3(H, E), threads, smem, stream>>>(proj, stride, q_off, f_off, v_off, f_bias, lower, out_w, eps, state,
-                                                    qs, ql, es, (T*)out, out_stride, H, D, V, DS, WHOLE, nullptr, nullptr, nullptr,
+                                                    qs, ql, es, (T*)out, out_stride, H, D, V, DS, nullptr, nullptr, nullptr,
                                                     max_chunks > 0 ? LONG : 0x7fffffff);
     if (max_chunks > 0) {
-        kern<<<dim3(H, E, max_chunks), threads, smem, stream>>>(proj, stride, q_off, f_off, v_off, f_bias, lower, out_w, eps,
-            state, qs, ql, es, (T*)out, out_stride, H, D, V, DS, LOCAL, chunk_state, chunk_decay, entry_chunk0, LONG);
+        kern_local<<<dim3(H, E, max_chunks), threads, smem, stream>>>(proj, stride, q_off, f_off, v_off, f_bias, lower, out_w, eps,
+            state, qs, ql, es, (T*)out, out_stride, H, D, V, DS, chunk_state, chunk_decay, entry_chunk0, LONG);
         hgrn2_chain_kernel<<<dim3(H, E, (D * V + 255) / 256), 256, 0, stream>>>(state, chunk_state, chunk_decay, ql, es, entry_chunk0, H, D, V);
-        kern<<<dim3(H, E, max_chunks), threads, smem, stream>>>(proj, stride, q_off, f_off, v_off, f_bias, lower, out_w, eps,
-            state, qs, ql, es, (T*)out, out_stride, H, D, V, DS, FROM_START, chunk_state, chunk_decay, entry_chunk0, LONG);
+        kern_from<<<dim3(H, E, max_chunks), threads, smem, stream>>>(proj, stride, q_off, f_off, v_off, f_bias, lower, out_w, eps,
+            state, qs, ql, es, (T*)out, out_stride, H, D, V, DS, chunk_state, chunk_decay, entry_chunk0, LONG);
     }
     return infero_check_launch("hgrn2_scan");
 }

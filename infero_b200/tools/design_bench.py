@@ -19,6 +19,7 @@ import sys
 import types
 
 SIZES = {
+    "t": dict(width=256, heads=4, kv=2, dim=32, vdim=64, experts=4, top=2, ff=64, shared=128, vocab=1000),     # for tests
     "s": dict(width=1024, heads=8, kv=2, dim=64, vdim=128, experts=16, top=4, ff=512, shared=1024, vocab=32000),
     "m": dict(width=2048, heads=16, kv=4, dim=64, vdim=128, experts=32, top=4, ff=768, shared=1536, vocab=32000),
     "l": dict(width=4096, heads=32, kv=8, dim=64, vdim=128, experts=64, top=8, ff=768, shared=2048, vocab=32000),

@@ -43,3 +43,18 @@ def test_timeline_of_a_decode_step():
 def test_one_kernel_alone():
     out = _run(["infero_b200.tools.kernel_bench", "attn_decode_fused", "--batch", "2", "--context", "512", "--reps", "3"])
     assert "attn_decode_fused:" in out and "us per launch" in out and "error flag" not in out
+
+
+def test_design_bench_prints_both_designs_and_the_kernels(capsys):
+    """``bench.py --designs`` at a size made for tests: both models step, every kernel row has a time."""
+    import json
+    from infero_b200.tools import design_bench
+    assert design_bench.main(["--sizes", "t", "--prompt", "600", "--context", "300", "--batch", "3", "--layers", "2",
+                              "--kernels-at", "t"]) == 0
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert line["bench"] == "designs" and set(line["sizes"]["t"]) == {"shape", "vufizen", "qwen2"}
+    for design in ("vufizen", "qwen2"):
+        assert line["sizes"]["t"][design]["prefill_tok_s"] > 0 and line["sizes"]["t"][design]["decode_tok_s"] > 0
+    rows = line["kernels"]["rows"]
+    assert {"diff_attention_prefill", "hgrn2_scan_prefill", "moe_experts_decode", "gated_norm_add_prefill"} <= set(rows)
+    assert all(r["us"] > 0 for r in rows.values())
