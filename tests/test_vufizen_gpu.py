@@ -338,6 +338,23 @@ def test_a_batch_equals_each_request_alone_bitwise_in_32_bit():
         assert np.array_equal(together[k], alone[k]), k
 
 
+@pytest.mark.parametrize("name,dtype", [("C", "float32"), ("A", "float32"), ("D", "bfloat16")])
+def test_long_portions_run_the_recurrence_by_chunks(name, dtype):
+    """Portions of 512 tokens and more take the chunk-parallel form of the recurrence (chunks of 128 side by side);
+    shorter ones beside them in the same step run whole.  Cut so that chunk edges fall inside, at and next to the ends
+    of portions."""
+    def steps(reqs):
+        (a, ta), (b, tb) = list(reqs.items())[:2]
+        return [{"step": 0, "entries": [{"id": a, "tokens": ta[:513], "want": [0, 127, 128, 129, 511, 512]},
+                                        {"id": b, "tokens": tb[:40], "want": [39]}], "end": []},
+                {"step": 1, "entries": [{"id": b, "tokens": tb[40:680], "want": [0, 87, 88, 639]},
+                                        {"id": a, "tokens": ta[513:514], "want": [0]}], "end": []},
+                {"step": 2, "entries": [{"id": a, "tokens": ta[514:], "want": list(range(len(ta) - 514))},
+                                        {"id": b, "tokens": tb[680:], "want": list(range(len(tb) - 680))}], "end": [a, b]}]
+    # (sums over 700 keys and a recurrence 700 tokens long: the 32-bit runs reach 4e-5 at the last positions)
+    _replay(name, dtype, steps, [530, 700], max_seqs=2, tol=1e-4 if dtype == "float32" else None)
+
+
 def test_three_hundred_single_tokens():
     _replay("B", "float32", lambda r: R.steps_tail_decode(r, tail=300), [310])
     _replay("D", "bfloat16", lambda r: R.steps_tail_decode(r, tail=300), [305])
