@@ -2,7 +2,8 @@ from .spec import (BlockSpec, FeedForwardSpec, MixerSpec, ModelSpec, NormSpec, P
                    ScheduleEntry)
 from .qwen2 import ConfigError, Qwen2Config
 from .vufizen import VufizenConfig
+from .gositar import GositarConfig
 from .engine_config import EngineConfig
 
 __all__ = ["BlockSpec", "FeedForwardSpec", "MixerSpec", "ModelSpec", "NormSpec", "PositionSpec",
-           "ScheduleEntry", "ConfigError", "Qwen2Config", "VufizenConfig", "EngineConfig"]
+           "ScheduleEntry", "ConfigError", "Qwen2Config", "VufizenConfig", "GositarConfig", "EngineConfig"]

@@ -43,8 +43,13 @@ HGRN2_NAMES = (("q", "mix.q"), ("f", "mix.f"), ("f_bias", "mix.f.b"), ("lower", 
                ("out_norm", "mix.norm"), ("o", "mix.o"))
 MOE_NAMES = (("expert", "mlp.e{}"), ("gate", "gate"), ("up", "up"), ("down", "down"), ("router", "mlp.router"),
              ("shared", "mlp.shared"), ("shared_gate", "mlp.shared.sg"))
-MIXER_NAMES = {"diff_attention": DIFF_ATTENTION_NAMES, "hgrn2": HGRN2_NAMES}
-FEED_FORWARD_NAMES = {"moe_swiglu": MOE_NAMES}
+LATENT_ATTENTION_NAMES = (("q", "mix.q"), ("down", "mix.dkv"), ("latent_norm", "mix.dkv.norm"), ("up_k", "mix.uk"),
+                          ("up_v", "mix.uv"), ("gate", "mix.g"), ("o", "mix.o"))
+RELU2_NAMES = (("up", "mlp.up"), ("down", "mlp.down"))
+MOE_GROUPED_NAMES = (("expert", "mlp.e{}"), ("gate", "gate"), ("up", "up"), ("down", "down"), ("router", "mlp.router"),
+                     ("correction", "mlp.correction"), ("shared", "mlp.shared"))
+MIXER_NAMES = {"diff_attention": DIFF_ATTENTION_NAMES, "hgrn2": HGRN2_NAMES, "latent_attention": LATENT_ATTENTION_NAMES}
+FEED_FORWARD_NAMES = {"moe_swiglu": MOE_NAMES, "relu2": RELU2_NAMES, "moe_grouped": MOE_GROUPED_NAMES}
 
 
 @dataclass(frozen=True)
@@ -54,16 +59,24 @@ class PositionSpec:
     kind "rope_neox": pairs (i, i + rotary_dim/2), angle = pos * theta^(-2i/rotary_dim)
     (crates/kernels/src/cu/ops.cu:488-523, crates/kernels/src/cpu/mod.rs:275-314).
     kind "rope_interleaved": the same angles on adjacent pairs (2i, 2i + 1).
+
+    ``yarn`` = (factor, original, fast, slow) stretches the long waves for contexts beyond the ``original`` length:
+    with n(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta) the pair index whose wave makes t turns over the
+    original length, lo = max(floor(n(fast)), 0), hi = min(ceil(n(slow)), rotary_dim - 1) and
+    ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i's frequency is f_i (1 - ramp_i) + f_i / factor * ramp_i,
+    and cos and sin are multiplied by 0.1 ln(factor) + 1.
     """
     kind: str
     theta: float
     rotary_dim: int
+    yarn: Optional[Tuple[float, float, float, float]] = None
 
 
 @dataclass(frozen=True)
 class NormSpec:
     """kind "rmsnorm": x * rsqrt(mean(x^2) + eps) * w (crates/kernels/src/cu/ops.cu:44-62).
-    kind "rmsnorm_scalar": the same with w a single stored number for all coordinates."""
+    kind "rmsnorm_scalar": the same with w a single stored number for all coordinates.
+    kind "layernorm": (x - mean(x)) * rsqrt(mean((x - mean(x))^2) + eps) * w, no bias."""
     kind: str
     dim: int
     eps: float
@@ -87,6 +100,13 @@ class MixerSpec:
     kind "hgrn2": a gated linear recurrence with a ``head_dim`` x ``value_dim`` state per head whose
     forget gate (bounded below by a stored vector) also scales what is written; the result of a head is
     RMS-normed over ``value_dim`` with a shared weight.  ``norm_eps`` is the eps of the norms inside a mixer.
+
+    kind "latent_attention": keys and values of all heads are made from one cached row per token: the input
+    product gives ``latent_dim`` numbers (RMS-normed with a weight: the latent c) and ``rot_dim`` more (a rotated key
+    part shared by all heads); head n's key is [Wuk_n c | that part] (``head_dim`` + ``rot_dim`` wide, like its
+    query), its value Wuv_n c (``value_dim`` wide).  ``position`` turns the ``rot_dim`` parts of queries and keys
+    (its ``rotary_dim`` <= ``rot_dim``).  ``out_gate``: head n's result is multiplied by sigmoid of the n-th row of
+    one more product of the mixer's input.  Causal softmax over all keys, ``scale`` as given.
     """
     kind: str
     hidden: int
@@ -103,6 +123,9 @@ class MixerSpec:
     qk_norm: bool = False
     norm_eps: float = 1e-6
     diff: float = 0.0
+    rot_dim: int = 0                  # latent attention: width of the rotated part of a query / key
+    latent_dim: int = 0               # latent attention: width of the cached latent
+    out_gate: bool = False            # latent attention: a sigmoid gate per head on the result
     # free-form extras for mixers defined outside the framework
     extra: Tuple[Tuple[str, object], ...] = ()
     # role -> leaf name under the block's prefix (see ATTENTION_NAMES); roles not given keep the default
@@ -130,13 +153,29 @@ class FeedForwardSpec:
     kind "moe_swiglu": ``experts`` SwiGLU experts of width ``intermediate`` of which every token uses the
     ``top`` with the largest router logits, weighted by the softmax over those logits alone; with
     ``shared_intermediate`` > 0 a SwiGLU expert of that width runs for every token and is added, times
-    sigmoid(w . x) of a stored vector w."""
+    sigmoid(w . x) of a stored vector w.
+
+    kind "relu2": down(relu(up(x))^2).
+
+    kind "moe_grouped": experts of the gated form down(glu(gate(x), up(x))) with ``activation`` "glu_clamped"
+    (g' = min(g, ``limit``), u' = clamp(u, -limit, limit), g' sigmoid(``act_alpha`` g') (u' + 1)) or "swiglu".  Routing:
+    s = softmax of the router's logits over all experts; experts are picked by s + a stored per-expert correction
+    (``route_correction``), among the ``route_keep`` best of ``route_groups`` groups of neighbouring experts (a
+    group's score: its largest pick score); weights are s of the ``top`` picked over their sum.  With
+    ``shared_intermediate`` > 0 an expert of that width (limit ``shared_limit``) runs for every token and is added."""
     kind: str
     hidden: int
     intermediate: int
     experts: int = 0
     top: int = 0
     shared_intermediate: int = 0
+    activation: str = "swiglu"
+    limit: float = 0.0
+    act_alpha: float = 1.0
+    shared_limit: float = 0.0
+    route_groups: int = 1
+    route_keep: int = 1
+    route_correction: bool = False
     extra: Tuple[Tuple[str, object], ...] = ()
     names: Tuple[Tuple[str, str], ...] = ()          # role -> leaf name (see SWIGLU_NAMES)
     weight_suffix: str = ".weight"
@@ -154,6 +193,9 @@ class BlockSpec:
     x += norm1(mixer(x) * sigmoid(G1 x + b1)); x += norm2(ffn(x) * sigmoid(G2 x + b2)); the gates are
     there where ``mixer_gate_name`` / ``ffn_gate_name`` are given (bias: that name + ``gate_bias_suffix``),
     and ``ffn`` may be None (a layer with a mixer only).
+    kind "hyper_prenorm": the residual is ``streams`` vectors per token.  Sublayer q (1: mixer, 2: feed-forward) has
+    three small tensors under ``hyper_names[q-1]``: ``.in`` [S], ``.mix`` [S, S] (from, to), ``.out`` [S];
+    u = sum_s in[s] x_s; y = sublayer(norm_q(u)); x_r <- sum_s mix[s, r] x_s + out[r] y for all r at once.
     """
     kind: str
     prefix: str
@@ -167,6 +209,8 @@ class BlockSpec:
     mixer_gate_name: Optional[str] = None
     ffn_gate_name: Optional[str] = None
     gate_bias_suffix: str = ".b"
+    streams: int = 0
+    hyper_names: Tuple[str, str] = ("hc1", "hc2")
 
 
 @dataclass(frozen=True)
@@ -199,6 +243,8 @@ class ModelSpec:
     eos_token_ids: Tuple[int, ...] = ()
     embed_scale: float = 1.0
     logit_scale: float = 1.0
+    streams: int = 0                  # > 0: the residual is this many vectors per token, all equal to the embedding at
+                                      # the start and added up in front of the final norm (blocks of kind "hyper_prenorm")
 
     def num_cache_slots(self) -> int:
         return 1 + max((e.cache for e in self.schedule), default=-1)

@@ -22,6 +22,19 @@ __device__ __forceinline__ float load_any(const void* p, int dtype, size_t i) {
     return dtype == INFERO_F32 ? ((const float*)p)[i] : __bfloat162float(((const bf16*)p)[i]);
 }
 
+// Gated activations of a feed-forward layer, from a gate g and an up value u:
+//   GLU_SILU:    silu(g) * u
+//   GLU_CLAMPED: g' = min(g, limit), u' = clamp(u, -limit, limit);  g' * sigmoid(alpha * g') * (u' + 1)
+enum : int { GLU_SILU = 0, GLU_CLAMPED = 1 };
+__device__ __forceinline__ float glu_act(float g, float u, int kind, float limit, float alpha) {
+    if (kind == GLU_CLAMPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    }
+    return g / (1.0f + expf(-g)) * u;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -429,7 +429,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 template <int EPI, typename OutT>
 __device__ __forceinline__ void drain_accumulator(uint32_t lane_addr, int ra, int b0, int BN, int RA, int RB,
                                                   OutT* __restrict__ out, const void* __restrict__ bias,
-                                                  int bias_dtype, long long ldc) {
+                                                  int bias_dtype, long long ldc, int act_kind = GLU_SILU,
+                                                  float act_limit = 0.f, float act_alpha = 1.f) {
     const int col_end = min(RB, b0 + BN);                // what this tile owns
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -449,7 +450,9 @@ __device__ __forceinline__ void drain_accumulator(uint32_t lane_addr, int ra, in
                     OutT* dst = out + (size_t)ra * ldc + (rb >> 1);
                     float h[8];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) h[e] = silu_mul(v[2 * e], v[2 * e + 1]);
+                    for (int e = 0; e < 8; ++e)
+                        h[e] = act_kind == GLU_SILU ? silu_mul(v[2 * e], v[2 * e + 1])
+                                                    : glu_act(v[2 * e], v[2 * e + 1], act_kind, act_limit, act_alpha);
                     if (rb + 16 <= RB && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 && sizeof(OutT) == 2) {
                         uint32_t pk[4];
 #pragma unroll
@@ -500,7 +503,7 @@ __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                           OutT* __restrict__ out, const void* __restrict__ bias, int bias_dtype,
                           int RA_bound, int RB, int K, long long ldc, int BN, int* __restrict__ err_flag,
-                          const int* __restrict__ tile_group) {
+                          const int* __restrict__ tile_group, int act_kind, float act_limit, float act_alpha) {
     // tile_group (or null): a grouped product.  map_b then covers several stacked [RB, K] matrices and the
     // 128-row tile m of the activations multiplies matrix tile_group[m] (a negative entry: a tile of padding
     // rows, multiplied with matrix 0).  The entry behind the last tile's holds the number of rows in use (the
@@ -662,7 +665,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[a], (uint32_t)(i >> 1) & 1u, abort_flag))) { ok = false; break; }
             tc_fence_after_sync();
             const uint32_t lane_addr = tmem_base + (uint32_t)a * PERS_MAX_BN + ((uint32_t)(q * 32) << 16);
-            drain_accumulator<EPI, OutT>(lane_addr, ra, b0, BN, RA, RB, out, bias, bias_dtype, ldc);
+            drain_accumulator<EPI, OutT>(lane_addr, ra, b0, BN, RA, RB, out, bias, bias_dtype, ldc, act_kind, act_limit, act_alpha);
             // this warp has read its quarter of the accumulator: hand it back
             tc_fence_before_sync();
             __syncwarp();
@@ -988,7 +991,8 @@ int pick_tile_n(int M, int N, int ctas, int multiple) {
 template <int EPI, typename OutT>
 int launch_persistent(const void* x, const void* w, void* out, const void* bias, int bias_dtype,
                       int RA, int RB, int K, int ldx, long long ldc, int sm_count, int* err, cudaStream_t stream,
-                      const int* tile_group = nullptr, int n_groups = 1) {
+                      const int* tile_group = nullptr, int n_groups = 1, int act_kind = GLU_SILU, float act_limit = 0.f,
+                      float act_alpha = 1.f) {
     using Plan = SmemPlan<PERS_MAX_BN, PERS_STAGES>;
     auto kern = gemm_tc_persistent_kernel<EPI, OutT>;
     static bool configured = false;
@@ -1008,7 +1012,7 @@ int launch_persistent(const void* x, const void* w, void* out, const void* bias,
     const int n_tiles = ((RA + TILE_A - 1) / TILE_A) * ((RB + bn - 1) / bn);
     const int ctas = n_tiles < sms ? n_tiles : sms;
     launch_pdl(kern, dim3(ctas), dim3(GEMM_THREADS), Plan::TOTAL, stream, ma, mb, (OutT*)out, bias, bias_dtype, RA, RB,
-               K, ldc, bn, err, tile_group);
+               K, ldc, bn, err, tile_group, act_kind, act_limit, act_alpha);
     return infero_check_launch("gemm_tc_persistent");
 }
 
@@ -1376,8 +1380,10 @@ int infero_gemm_tc_swiglu(const void* x, const void* w, void* out, int M, int N,
 // A grouped product on the persistent kernel: x [M, K] in tiles of 128 rows, w n_groups stacked [N, K] matrices,
 // tile m of x multiplies matrix tile_group[m] (device int32 [ceil(M / 128)]).  swiglu: w's rows alternate gate and
 // up and out is bf16 [M, N / 2]; else out is float32 [M, N].
+// With a gated activation the pair (gate, up) goes through glu_act(act_kind, act_limit, act_alpha) of common.cuh.
 int infero_gemm_tc_grouped(const void* x, const void* w, void* out, int swiglu, int M, int N, int K, int ldx, int ldc,
-                           const int* tile_group, int n_groups, int sm_count, cudaStream_t stream) {
+                           const int* tile_group, int n_groups, int sm_count, int act_kind, float act_limit,
+                           float act_alpha, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     INFERO_REQUIRE(infero_gemm_tc_supported(x, w, M, N, K, ldx), "gemm_tc_grouped: shape M=%d N=%d K=%d ldx=%d not supported", M, N, K, ldx);
     INFERO_REQUIRE(tile_group && n_groups >= 1 && (long long)N * n_groups < (1ll << 31), "gemm_tc_grouped: bad groups");
@@ -1386,7 +1392,7 @@ int infero_gemm_tc_grouped(const void* x, const void* w, void* out, int swiglu, 
     if (swiglu) {
         INFERO_REQUIRE(N % 2 == 0 && ldc >= N / 2, "gemm_tc_grouped: N=%d must be even and ldc=%d at least N/2", N, ldc);
         return launch_persistent<EPI_ROW_SWIGLU, bf16>(x, w, out, nullptr, 0, M, N, K, ldx, ldc, sm_count, err, stream,
-                                                       tile_group, n_groups);
+                                                       tile_group, n_groups, act_kind, act_limit, act_alpha);
     }
     INFERO_REQUIRE(ldc >= N, "gemm_tc_grouped: ldc=%d below N=%d", ldc, N);
     return launch_persistent<EPI_ROW, float>(x, w, out, nullptr, 0, M, N, K, ldx, ldc, sm_count, err, stream, tile_group,

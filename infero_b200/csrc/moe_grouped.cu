@@ -4,7 +4,7 @@
 //   tiles of 64 or 128 rows, so a tile belongs to one expert.  sorted_pair[r] is the pair (token * top + choice) in row
 //   r, or -1 in padding; tile_expert[m] the expert of tile m, or -1 behind the last one.  The number of
 //   tiles launched is a bound known on the host: ceil((pairs + experts * (rows - 1)) / rows).
-// up:   act[r, j] = silu(h_tok(r) . Wg_e[j]) * (h_tok(r) . Wu_e[j]) from the stacked [E, 2 ff, d] matrix whose
+// up:   act[r, j] = glu(h_tok(r) . Wg_e[j], h_tok(r) . Wu_e[j]) (a gated activation of common.cuh) from the stacked [E, 2 ff, d] matrix whose
 //       rows alternate gate_j, up_j: an accumulator's adjacent columns are such a pair.
 // down: part[pair(r), i] = act[r] . Wd_e[i]     (float32 [tokens * top, d])
 // combine: y[t] = sum_c w[t, c] * part[t * top + c] (+ gate[t] * shared[t]), choices in ascending order.
@@ -95,7 +95,7 @@ template <int EPI, int TM, int TN, int WM, int WN, int STAGES>
 __global__ void __launch_bounds__(WM * WN * 32)
 grouped_gemm_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ a_rows, const bf16* __restrict__ B,
                     const int* __restrict__ tile_expert, int N, int K, void* __restrict__ out, int ldo,
-                    const int* __restrict__ out_rows) {
+                    const int* __restrict__ out_rows, int act_kind, float act_limit, float act_alpha) {
     constexpr int NT = WM * WN * 32, MI = TM / WM / 16, NI = TN / WN / 8;
     extern __shared__ __align__(16) uint8_t gsm[];
     bf16* As = reinterpret_cast<bf16*>(gsm);                    // [STAGES][TM * LDS]
@@ -173,8 +173,8 @@ grouped_gemm_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__
                 const int col = nt * TN + wn * NI * 8 + n8 * 8 + c * 2;      // even: gate, col + 1: up
                 if (col + 1 < N) {
                     const float g0 = acc[i][n8][0], u0 = acc[i][n8][1], g1 = acc[i][n8][2], u1 = acc[i][n8][3];
-                    o[(size_t)r0 * ldo + col / 2] = __float2bfloat16_rn(g0 / (1.0f + expf(-g0)) * u0);
-                    o[(size_t)r1 * ldo + col / 2] = __float2bfloat16_rn(g1 / (1.0f + expf(-g1)) * u1);
+                    o[(size_t)r0 * ldo + col / 2] = __float2bfloat16_rn(glu_act(g0, u0, act_kind, act_limit, act_alpha));
+                    o[(size_t)r1 * ldo + col / 2] = __float2bfloat16_rn(glu_act(g1, u1, act_kind, act_limit, act_alpha));
                 }
             }
         } else {
@@ -198,11 +198,13 @@ grouped_gemm_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__
 
 template <int EPI, int TM, int TN, int WM, int WN, int STAGES>
 void launch_grouped(const bf16* A, int lda, const int* a_rows, const bf16* B, const int* tile_expert, int tiles, int N, int K,
-                    void* out, int ldo, const int* out_rows, cudaStream_t stream) {
+                    void* out, int ldo, const int* out_rows, cudaStream_t stream, int act_kind = GLU_SILU, float act_limit = 0.f,
+                    float act_alpha = 1.f) {
     auto kern = grouped_gemm_kernel<EPI, TM, TN, WM, WN, STAGES>;
     const int smem = STAGES * (TM + TN) * LDS * 2;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    kern<<<dim3(tiles, (N + TN - 1) / TN), WM * WN * 32, smem, stream>>>(A, lda, a_rows, B, tile_expert, N, K, out, ldo, out_rows);
+    kern<<<dim3(tiles, (N + TN - 1) / TN), WM * WN * 32, smem, stream>>>(A, lda, a_rows, B, tile_expert, N, K, out, ldo, out_rows,
+                                                                         act_kind, act_limit, act_alpha);
 }
 
 __global__ void moe_combine_kernel(const float* __restrict__ part, const float* __restrict__ top_w,
@@ -233,7 +235,7 @@ int infero_moe_grouped_tiles(int n_pairs, int E) {
 int infero_moe_experts_grouped(const void* h, int h_stride, const void* gate_up, const void* down, const int* top_idx,
                                const float* top_w, const float* shared, const float* shared_gate, int* sorted_pair,
                                int* a_rows, int* tile_expert, void* act, float* part, float* y, int n_tokens, int d,
-                               int ff, int E, int top, cudaStream_t stream) {
+                               int ff, int E, int top, int act_kind, float act_limit, float act_alpha, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     INFERO_REQUIRE(d % 8 == 0 && ff % 8 == 0 && h_stride % 8 == 0, "moe grouped: widths %d / %d must be multiples of 8", d, ff);
     const int n_pairs = n_tokens * top, tiles = infero_moe_grouped_tiles(n_pairs, E);
@@ -243,12 +245,12 @@ int infero_moe_experts_grouped(const void* h, int h_stride, const void* gate_up,
     moe_align_kernel<<<1, 1024, sh, stream>>>(top_idx, n_pairs, E, top, sorted_pair, tile_expert, tiles, a_rows, BM, nullptr);
     if (BM == 128) {
         launch_grouped<EPI_SWIGLU, 128, 128, 4, 2, 3>((const bf16*)h, h_stride, a_rows, (const bf16*)gate_up, tile_expert, tiles,
-                                                      2 * ff, d, act, ff, nullptr, stream);
+                                                      2 * ff, d, act, ff, nullptr, stream, act_kind, act_limit, act_alpha);
         launch_grouped<EPI_SCATTER, 128, 128, 4, 2, 3>((const bf16*)act, ff, nullptr, (const bf16*)down, tile_expert, tiles,
                                                        d, ff, part, d, sorted_pair, stream);
     } else {
         launch_grouped<EPI_SWIGLU, 64, 64, 4, 1, 2>((const bf16*)h, h_stride, a_rows, (const bf16*)gate_up, tile_expert, tiles,
-                                                    2 * ff, d, act, ff, nullptr, stream);
+                                                    2 * ff, d, act, ff, nullptr, stream, act_kind, act_limit, act_alpha);
         launch_grouped<EPI_SCATTER, 64, 64, 4, 1, 2>((const bf16*)act, ff, nullptr, (const bf16*)down, tile_expert, tiles,
                                                      d, ff, part, d, sorted_pair, stream);
     }

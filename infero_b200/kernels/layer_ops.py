@@ -156,7 +156,18 @@ def moe_select(logits: torch.Tensor, E: int, top: int, gate_col: int = -1):
     return idx, w, gate
 
 
-def moe_experts_streamed(h, gate_up, down, top_idx, top_w, shared, shared_gate, y) -> None:
+GLU_KINDS = {"swiglu": 0, "glu_clamped": 1}
+
+
+def _act_args(act):
+    """(kind, limit, alpha) of a gated activation as the kernels take it; None: silu(g) * u."""
+    if act is None:
+        return c_int(0), c_float(0.0), c_float(1.0)
+    kind, limit, alpha = act
+    return c_int(GLU_KINDS[kind]), c_float(limit), c_float(alpha)
+
+
+def moe_experts_streamed(h, gate_up, down, top_idx, top_w, shared, shared_gate, y, act=None) -> None:
     """y[t] = sum_c top_w[t, c] * expert_{top_idx[t, c]}(h[t]) (+ shared_gate[t] * shared[t]); every (token,
     choice) streams its expert's rows.  gate_up [E, 2 ff, d] (rows alternate gate_j, up_j), down [E, d, ff]."""
     T, d = h.shape
@@ -164,14 +175,15 @@ def moe_experts_streamed(h, gate_up, down, top_idx, top_w, shared, shared_gate, 
     ff, top = ff2 // 2, top_idx.shape[1]
     assert gate_up.dtype == h.dtype == down.dtype and gate_up.is_contiguous() and down.is_contiguous()
     assert tuple(down.shape) == (E, d, ff) and y.dtype == torch.float32 and y.is_contiguous() and y.shape == (T, d)
-    act = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
+    scratch = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
     _check(lib().infero_moe_experts_streamed(_ptr(h), c_int(h.stride(0)), _ptr(gate_up), _ptr(down), c_int(_dt(h)),
                                              _ptr(_i32(top_idx, "top_idx")), _ptr(_f32(top_w, "top_w")),
                                              _ptr(_f32(shared, "shared")), _ptr(_f32(shared_gate, "shared_gate")),
-                                             _ptr(act), _ptr(y), c_int(T), c_int(d), c_int(ff), c_int(top), _stream()))
+                                             _ptr(scratch), _ptr(y), c_int(T), c_int(d), c_int(ff), c_int(top),
+                                             *_act_args(act), _stream()))
 
 
-def moe_experts_grouped(h, gate_up, down, top_idx, top_w, shared, shared_gate, y) -> None:
+def moe_experts_grouped(h, gate_up, down, top_idx, top_w, shared, shared_gate, y, act=None) -> None:
     """The same result as ``moe_experts_streamed`` by grouped tensor-core products (bf16): the (token, choice)
     pairs are sorted by expert into 64-row tiles; see csrc/moe_grouped.cu."""
     T, d = h.shape
@@ -185,16 +197,17 @@ def moe_experts_grouped(h, gate_up, down, top_idx, top_w, shared, shared_gate, y
     dev = h.device
     ints = torch.empty(2 * R + tiles + 1, dtype=torch.int32, device=dev)
     sorted_pair, a_rows, tile_expert = ints[:R], ints[R:2 * R], ints[2 * R:]
-    act = torch.empty((R, ff), dtype=torch.bfloat16, device=dev)
+    scratch = torch.empty((R, ff), dtype=torch.bfloat16, device=dev)
     part = torch.empty((T * top, d), dtype=torch.float32, device=dev)
     _check(lib().infero_moe_experts_grouped(_ptr(h), c_int(h.stride(0)), _ptr(gate_up), _ptr(down),
                                             _ptr(_i32(top_idx, "top_idx")), _ptr(_f32(top_w, "top_w")),
                                             _ptr(_f32(shared, "shared")), _ptr(_f32(shared_gate, "shared_gate")),
-                                            _ptr(sorted_pair), _ptr(a_rows), _ptr(tile_expert), _ptr(act), _ptr(part),
-                                            _ptr(y), c_int(T), c_int(d), c_int(ff), c_int(E), c_int(top), _stream()))
+                                            _ptr(sorted_pair), _ptr(a_rows), _ptr(tile_expert), _ptr(scratch), _ptr(part),
+                                            _ptr(y), c_int(T), c_int(d), c_int(ff), c_int(E), c_int(top), *_act_args(act),
+                                            _stream()))
 
 
-def moe_experts_tc(h, gate_up, down, top_idx, top_w, shared, shared_gate, y) -> None:
+def moe_experts_tc(h, gate_up, down, top_idx, top_w, shared, shared_gate, y, act=None) -> None:
     """The same result by grouped products on the tcgen05 kernel: the tokens' rows are copied into expert order in
     tiles of 128 rows, two grouped products (the first with the SwiGLU epilogue) run over them, and the rows of a
     token's choices are added up in ascending order; see csrc/moe_grouped.cu and ``infero_gemm_tc_grouped``."""
@@ -213,13 +226,101 @@ def moe_experts_tc(h, gate_up, down, top_idx, top_w, shared, shared_gate, y) -> 
     _check(lib().infero_moe_tc_prepare(_ptr(h), c_int(h.stride(0)), _ptr(_i32(top_idx, "top_idx")), _ptr(sorted_pair),
                                        _ptr(a_rows), _ptr(tile_expert), _ptr(pair_row), _ptr(xs), c_int(T), c_int(d),
                                        c_int(E), c_int(top), _stream()))
-    act = torch.empty((R, ff), dtype=torch.bfloat16, device=dev)
+    scratch = torch.empty((R, ff), dtype=torch.bfloat16, device=dev)
     sms = sm_count(dev)
-    _check(lib().infero_gemm_tc_grouped(_ptr(xs), _ptr(gate_up), _ptr(act), c_int(1), c_int(R), c_int(2 * ff), c_int(d),
-                                        c_int(d), c_int(ff), _ptr(tile_expert), c_int(E), c_int(sms), _stream()))
+    _check(lib().infero_gemm_tc_grouped(_ptr(xs), _ptr(gate_up), _ptr(scratch), c_int(1), c_int(R), c_int(2 * ff), c_int(d),
+                                        c_int(d), c_int(ff), _ptr(tile_expert), c_int(E), c_int(sms), *_act_args(act),
+                                        _stream()))
     rows = torch.empty((R, d), dtype=torch.float32, device=dev)
-    _check(lib().infero_gemm_tc_grouped(_ptr(act), _ptr(down), _ptr(rows), c_int(0), c_int(R), c_int(d), c_int(ff),
-                                        c_int(ff), c_int(d), _ptr(tile_expert), c_int(E), c_int(sms), _stream()))
+    _check(lib().infero_gemm_tc_grouped(_ptr(scratch), _ptr(down), _ptr(rows), c_int(0), c_int(R), c_int(d), c_int(ff),
+                                        c_int(ff), c_int(d), _ptr(tile_expert), c_int(E), c_int(sms), *_act_args(None),
+                                        _stream()))
     _check(lib().infero_moe_tc_combine(_ptr(rows), _ptr(pair_row), _ptr(_f32(top_w, "top_w")), _ptr(_f32(shared, "shared")),
                                        _ptr(_f32(shared_gate, "shared_gate")), _ptr(y), c_int(T), c_int(d), c_int(top),
                                        _stream()))
+
+
+def moe_select_grouped(logits: torch.Tensor, correction: Optional[torch.Tensor], E: int, top: int, groups: int = 1,
+                       keep: int = 1):
+    """From float32 logits [T, >= E]: s = softmax over the E experts; the ``top`` largest of s + correction among the
+    ``keep`` best of ``groups`` groups of neighbouring experts; (top_idx int32 [T, top], top_w float32 [T, top]) with
+    top_w = s of the chosen over their sum.  See csrc/moe.cu."""
+    T = logits.shape[0]
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[1] >= E
+    assert correction is None or correction.numel() == E
+    idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    _check(lib().infero_moe_select_grouped(_ptr(logits), c_int(logits.stride(0)), _ptr(_f32(correction, "correction")),
+                                           _ptr(idx), _ptr(w), c_int(T), c_int(E), c_int(top), c_int(groups), c_int(keep),
+                                           _stream()))
+    return idx, w
+
+
+def _product_in(v):
+    """(pointer source, dtype tag, splits, split stride, shape) of a product given as a tensor or as partial sums."""
+    from . import Partials
+    if isinstance(v, Partials):
+        assert v.bias is None
+        return v.data, 0, v.splits, v.split_stride, tuple(v.shape)
+    assert v.is_contiguous()
+    return v, _dt(v), 1, 0, tuple(v.shape)
+
+
+def glu_act(gate_up, out: torch.Tensor, act=None) -> None:
+    """out[t, j] = glu(g[t, 2j], g[t, 2j + 1]) for g = gate_up (a tensor or ``Partials``; gate and up alternate along a
+    row); ``act`` = (kind, limit, alpha), None: silu(g) * u."""
+    T, ff = out.shape
+    data, dt, splits, stride, shape = _product_in(gate_up)
+    assert shape == (T, 2 * ff) and out.is_contiguous()
+    _check(lib().infero_glu_act(_ptr(data), c_int(dt), c_int(splits), c_longlong(stride), _ptr(out), c_int(_dt(out)), c_int(T),
+                                c_int(ff), *_act_args(act), _stream()))
+
+
+def relu2(v, out: torch.Tensor) -> None:
+    """out = max(v, 0)^2, v a tensor or ``Partials`` of out's shape."""
+    T, ff = out.shape
+    data, dt, splits, stride, shape = _product_in(v)
+    assert shape == (T, ff) and out.is_contiguous()
+    _check(lib().infero_relu2(_ptr(data), c_int(dt), c_int(splits), c_longlong(stride), _ptr(out), c_int(_dt(out)), c_int(T),
+                              c_int(ff), _stream()))
+
+
+def add_layernorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor,
+                  rows: Optional[torch.Tensor] = None) -> None:
+    """x += delta (float32, if given); out = layer norm of x (weight, no bias).  With ``rows`` only those rows are
+    normalised and x is left as it is."""
+    d = x.shape[1]
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape[1] == d
+    assert delta is None or (delta.dtype == torch.float32 and delta.is_contiguous() and delta.shape == x.shape)
+    n = out.shape[0]
+    assert n == (x.shape[0] if rows is None else rows.numel()) and weight.numel() == d
+    _check(lib().infero_add_layernorm(_ptr(x), _ptr(delta), _ptr(_f32(weight, "weight")), c_float(eps), _ptr(out),
+                                      c_int(_dt(out)), _ptr(None if rows is None else _i32(rows, "rows")), c_int(n), c_int(d),
+                                      _stream()))
+
+
+def hyper_step(xs: torch.Tensor, y: Optional[torch.Tensor], mix: Optional[torch.Tensor], w_out: Optional[torch.Tensor],
+               w_in: Optional[torch.Tensor], norm_w: Optional[torch.Tensor], eps: float, h_out: Optional[torch.Tensor],
+               u_out: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> None:
+    """One pass over the streams xs (float32 [T, S, d]) of every token: with ``y`` (float32 [T, d]) the update
+    xs[r] <- sum_s mix[s, r] xs[s] + w_out[r] y; with ``w_in`` and ``norm_w`` the next sublayer's input
+    h_out = layer norm(sum_s w_in[s] xs[s]); with ``u_out`` (float32) and no norm the weighted sum itself (w_in None:
+    the plain sum).  ``rows``: work on these tokens only."""
+    T, S, d = xs.shape
+    assert xs.dtype == torch.float32 and xs.is_contiguous()
+    assert y is None or (y.dtype == torch.float32 and y.shape == (T, d) and y.stride(1) == 1)
+    n = T if rows is None else rows.numel()
+    for o in (h_out, u_out):
+        assert o is None or (o.is_contiguous() and tuple(o.shape) == (n, d))
+    assert u_out is None or u_out.dtype == torch.float32
+    _check(lib().infero_hyper_step(_ptr(xs), _ptr(y), c_int(y.stride(0) if y is not None else 0), _ptr(_f32(mix, "mix")),
+                                   _ptr(_f32(w_out, "w_out")), _ptr(_f32(w_in, "w_in")), _ptr(_f32(norm_w, "norm_w")),
+                                   c_float(eps), _ptr(h_out), c_int(_dt(h_out) if h_out is not None else 0), _ptr(u_out),
+                                   _ptr(None if rows is None else _i32(rows, "rows")), c_int(n), c_int(S), c_int(d), _stream()))
+
+
+def streams_fill(x: torch.Tensor, xs: torch.Tensor) -> None:
+    """xs[t, s] = x[t] for every stream s."""
+    T, S, d = xs.shape
+    assert x.dtype == xs.dtype == torch.float32 and x.is_contiguous() and xs.is_contiguous() and tuple(x.shape) == (T, d)
+    _check(lib().infero_streams_fill(_ptr(x), _ptr(xs), c_int(T), c_int(S), c_int(d), _stream()))

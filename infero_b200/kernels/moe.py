@@ -17,7 +17,8 @@ GROUPED_FROM = int(os.environ.get("INFERO_MOE_GROUPED_FROM", "5"))     # tokens 
 TC_PAIRS_PER_EXPERT = int(os.environ.get("INFERO_MOE_TC_FROM", "96"))  # pairs per expert from which tcgen05 tiles pay
 
 
-def experts(h, gate_up, down, top_idx, top_w, shared, shared_gate, y) -> None:
+def experts(h, gate_up, down, top_idx, top_w, shared, shared_gate, y, act=None) -> None:
+    """``act``: the experts' gated activation as (kind, limit, alpha) (``layer_ops.GLU_KINDS``); None: silu(g) * u."""
     T, d = h.shape
     ff = gate_up.shape[1] // 2
     E, top = gate_up.shape[0], top_idx.shape[1]
@@ -26,9 +27,9 @@ def experts(h, gate_up, down, top_idx, top_w, shared, shared_gate, y) -> None:
     if (h.dtype == torch.bfloat16 and T >= GROUPED_FROM and T * top > E and d % 8 == 0 and ff % 8 == 0
             and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0):
         if T * top >= TC_PAIRS_PER_EXPERT * E and gate_up.data_ptr() % 16 == 0 and down.data_ptr() % 16 == 0:
-            L.moe_experts_tc(h, gate_up, down, top_idx, top_w, shared, shared_gate, y)
+            L.moe_experts_tc(h, gate_up, down, top_idx, top_w, shared, shared_gate, y, act)
         else:
-            L.moe_experts_grouped(h, gate_up, down, top_idx, top_w, shared, shared_gate, y)
+            L.moe_experts_grouped(h, gate_up, down, top_idx, top_w, shared, shared_gate, y, act)
         return
     # the streaming kernels index (token, choice) pairs by a grid dimension of at most 65,535
     step = max(1, 65535 // top_idx.shape[1])
@@ -36,4 +37,4 @@ def experts(h, gate_up, down, top_idx, top_w, shared, shared_gate, y) -> None:
         b = min(T, a + step)
         L.moe_experts_streamed(h[a:b], gate_up, down, top_idx[a:b], top_w[a:b],
                                None if shared is None else shared[a:b], None if shared_gate is None else shared_gate[a:b],
-                               y[a:b])
+                               y[a:b], act)

@@ -28,6 +28,8 @@ class DecoderModel:
         self.embed: Optional[torch.Tensor] = None
         self.head: Optional[Linear] = None
         self._native = None                  # the native launcher of a whole step, made at first use
+        if any(getattr(b, "streams", 0) != spec.streams for b in spec.blocks):
+            raise ValueError(f"the model keeps {spec.streams or 'no'} streams; every block has to keep as many")
         for e in spec.schedule:
             if not (0 <= e.block < len(self.blocks)):
                 raise ValueError(f"schedule names block {e.block}, model has {len(self.blocks)}")
@@ -103,6 +105,34 @@ class DecoderModel:
         add(self.final_norm.weight)
         return total
 
+    def _forward_streams(self, ctx, x0: torch.Tensor, logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """The schedule on a residual of ``spec.streams`` vectors per token (float32 [T, S, d]), all equal to the
+        embedding at the start; a block returns the update of its last sublayer, which the next block applies in
+        its first pass over the streams; at the end the streams are added up (on the wanted rows only)."""
+        from ..kernels import layer_ops as L
+        s = self.spec
+        T = x0.shape[0]
+        x = torch.empty((T, s.streams, s.hidden), dtype=torch.float32, device=x0.device)
+        L.streams_fill(x0, x)
+        pending = None
+        for i, entry in enumerate(s.schedule):
+            ctx.upcoming = None
+            ctx.schedule_index = i
+            pending = self.blocks[entry.block].forward(ctx, x, pending, entry)
+        if logit_rows is None or logit_rows.numel() == 0:
+            return None
+        R = logit_rows.numel()
+        total = torch.empty((R, s.hidden), dtype=torch.float32, device=x0.device)
+        if pending is not None:
+            L.hyper_step(x, pending[0], pending[1], pending[2], None, None, 0.0, None, u_out=total, rows=logit_rows)
+        else:
+            L.hyper_step(x, None, None, None, None, None, 0.0, None, u_out=total, rows=logit_rows)
+        h = self.final_norm.forward(ctx, total, None)
+        logits = self.head.forward(h, out_dtype=torch.float32)
+        if s.logit_scale != 1.0:
+            logits.mul_(s.logit_scale)
+        return logits
+
     # ---- one pass over the tokens of a step -------------------------------------------------
     def forward(self, ctx, token_ids: torch.Tensor, logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """token_ids int32 [T] on the device; logit_rows int32 [R] (indices into the T tokens)
@@ -118,6 +148,8 @@ class DecoderModel:
         T = token_ids.numel()
         x = torch.empty((T, s.hidden), dtype=torch.float32, device=token_ids.device)
         K.embed_gather(self.embed, token_ids, x, s.embed_scale, getattr(ctx, "device_tokens", None))
+        if s.streams:
+            return self._forward_streams(ctx, x, logit_rows)
         delta = None
         for i, entry in enumerate(s.schedule):
             # a block may look at what runs after it (the built-in block folds the next block's first norm

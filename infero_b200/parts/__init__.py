@@ -3,14 +3,15 @@ from ..registry import register_part
 from .base import (FeedForward, KvCacheSpec, Mixer, Norm, Part, PositionEncoding, StateSpec,
                    TensorDecl)
 from .linear import Linear
-from .norm import RmsNorm, ScalarRmsNorm
+from .norm import LayerNorm, RmsNorm, ScalarRmsNorm
 from .rope import RopeInterleaved, RopeNeox
-from .mlp import SwiGluMlp
+from .mlp import GluMlp, Relu2Mlp, SwiGluMlp
 from .attention import GqaAttention
 from .hgrn2 import Hgrn2Mixer
 from .diff_attention import DiffAttention
-from .moe import MoeSwiGlu
-from .block import GatedPostNormBlock, PreNormBlock
+from .moe import GroupedMoe, MoeSwiGlu
+from .latent_attention import LatentAttention
+from .block import GatedPostNormBlock, HyperPreNormBlock, PreNormBlock
 
 register_part("norm", "rmsnorm", RmsNorm)
 register_part("position", "rope_neox", RopeNeox)
@@ -23,7 +24,14 @@ register_part("mixer", "hgrn2", Hgrn2Mixer)
 register_part("mixer", "diff_attention", DiffAttention)
 register_part("feed_forward", "moe_swiglu", MoeSwiGlu)
 register_part("block", "gated_postnorm", GatedPostNormBlock)
+register_part("norm", "layernorm", LayerNorm)
+register_part("mixer", "latent_attention", LatentAttention)
+register_part("feed_forward", "relu2", Relu2Mlp)
+register_part("feed_forward", "glu", GluMlp)
+register_part("feed_forward", "moe_grouped", GroupedMoe)
+register_part("block", "hyper_prenorm", HyperPreNormBlock)
 
 __all__ = ["FeedForward", "KvCacheSpec", "Mixer", "Norm", "Part", "PositionEncoding", "StateSpec",
            "TensorDecl", "Linear", "RmsNorm", "ScalarRmsNorm", "RopeNeox", "RopeInterleaved", "SwiGluMlp", "GqaAttention",
-           "Hgrn2Mixer", "DiffAttention", "MoeSwiGlu", "PreNormBlock", "GatedPostNormBlock"]
+           "Hgrn2Mixer", "DiffAttention", "MoeSwiGlu", "PreNormBlock", "GatedPostNormBlock", "LayerNorm", "GluMlp", "Relu2Mlp",
+           "GroupedMoe", "LatentAttention", "HyperPreNormBlock"]

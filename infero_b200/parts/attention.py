@@ -33,6 +33,8 @@ class GqaAttention(Mixer):
         self.rope = None
         if spec.position is not None:
             self.rope = part_class("position", spec.position.kind)(spec.position)
+            if getattr(self.rope, "amplitude", 1.0) != 1.0:
+                raise ValueError("this mixer's rotary kernel has no amplitude; the position table needs one")
         self.qkv: Linear = None
         self.out: Linear = None
         self.names = spec.tensor_names()

@@ -23,12 +23,14 @@ class PreNormBlock(Part):
         p = spec.prefix
         self.mixer_norm = part_class("norm", spec.mixer_norm.kind)(spec.mixer_norm, f"{p}.{spec.mixer_norm_name}")
         self.mixer = part_class("mixer", spec.mixer.kind)(spec.mixer, p)
-        self.ffn_norm = part_class("norm", spec.ffn_norm.kind)(spec.ffn_norm, f"{p}.{spec.ffn_norm_name}")
-        self.ffn = part_class("feed_forward", spec.ffn.kind)(spec.ffn, p)
+        self.ffn = self.ffn_norm = None      # a layer may have a mixer only
+        if spec.ffn is not None:
+            self.ffn_norm = part_class("norm", spec.ffn_norm.kind)(spec.ffn_norm, f"{p}.{spec.ffn_norm_name}")
+            self.ffn = part_class("feed_forward", spec.ffn.kind)(spec.ffn, p)
         self._native = None                  # the native launcher of this block, made at first use
 
     def parts(self):
-        return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None]
 
     def declare(self) -> List[TensorDecl]:
         out: List[TensorDecl] = []
@@ -60,6 +62,8 @@ class PreNormBlock(Part):
             delta = delta.as_partials()
         h = self.mixer_norm.forward(ctx, x, delta)
         a = self.mixer.forward(ctx, h, slot)
+        if self.ffn is None:
+            return a
         h = self.ffn_norm.forward(ctx, x, a)
         return self.ffn.forward(ctx, h)
 
@@ -164,3 +168,89 @@ class GatedPostNormBlock(Part):
             h = self._half(ctx, x, h, y, 1, self.ffn_norm)
         ctx._resid_act = (getattr(ctx, "schedule_index", -2), h)
         return None
+
+
+class HyperPreNormBlock(Part):
+    """A pre-norm layer whose residual is S streams per token (x float32 [T, S, d]).  For each sublayer (mixer, then
+    feed-forward if there is one) with its small tensors ``in`` [S], ``mix`` [S, S] (from, to) and ``out`` [S]:
+
+        u = sum_s in[s] x_s;   y = sublayer(norm(u));   x_r <- sum_s mix[s, r] x_s + out[r] y   (all r from the old x)
+
+    with norms of kind "layernorm".  One kernel per sublayer does the update for the sublayer before and the weighted
+    sum and norm for the next one (``hyper_step``); the update of a layer's last sublayer is left pending and done by
+    the next block of this kind in its first pass, or by the model in front of the final norm (``pending`` /
+    ``flush``).  The small tensors are float32 on both precisions."""
+
+    def __init__(self, spec: BlockSpec):
+        self.spec = spec
+        p = spec.prefix
+        self.S = int(spec.streams)
+        if self.S < 1:
+            raise ValueError("a hyper-connection block needs at least one stream")
+        self.mixer_norm = part_class("norm", spec.mixer_norm.kind)(spec.mixer_norm, f"{p}.{spec.mixer_norm_name}")
+        self.mixer = part_class("mixer", spec.mixer.kind)(spec.mixer, p)
+        self.ffn = self.ffn_norm = None
+        if spec.ffn is not None:
+            self.ffn_norm = part_class("norm", spec.ffn_norm.kind)(spec.ffn_norm, f"{p}.{spec.ffn_norm_name}")
+            self.ffn = part_class("feed_forward", spec.ffn.kind)(spec.ffn, p)
+        for n in (self.mixer_norm, self.ffn_norm):
+            if n is not None and n.spec.kind != "layernorm":
+                raise ValueError("a hyper-connection block takes layer norms")
+        self.hc = [None, None]               # per sublayer: (in, mix, out), float32
+
+    def parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None]
+
+    def _hc_names(self):
+        p, names = self.spec.prefix, self.spec.hyper_names
+        return [f"{p}.{names[0]}"] + ([f"{p}.{names[1]}"] if self.ffn is not None else [])
+
+    def declare(self) -> List[TensorDecl]:
+        out: List[TensorDecl] = []
+        for part in self.parts():
+            out += part.declare()
+        S = self.S
+        for n in self._hc_names():
+            out += [TensorDecl(f"{n}.in", (S,), role="bias", init="ones"), TensorDecl(f"{n}.out", (S,), role="bias", init="ones"),
+                    TensorDecl(f"{n}.mix", (S, S), role="bias")]
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for part in self.parts():
+            part.bind(tensors)
+        for i, n in enumerate(self._hc_names()):
+            self.hc[i] = tuple(tensors[f"{n}.{leaf}"].float().contiguous() for leaf in ("in", "mix", "out"))
+
+    @staticmethod
+    def _as_f32(y):
+        from .. import kernels as K
+        if hasattr(y, "as_partials"):
+            y = y.as_partials()
+        if isinstance(y, K.Partials):
+            return y.materialize(torch.float32)
+        return y if y.dtype == torch.float32 else y.float()
+
+    def forward(self, ctx, x, delta, slot):
+        from ..kernels import layer_ops as L
+        T, S, d = x.shape
+        assert S == self.S, f"the model keeps {S} streams, this block {self.S}"
+        pend = delta                          # (y, mix, out) of the sublayer that ran last, or None
+        eps = self.mixer_norm.spec.eps
+        h = torch.empty((T, d), dtype=ctx.act_dtype, device=x.device)
+        w_in, mix, w_out = self.hc[0]
+        L.hyper_step(x, *(pend if pend is not None else (None, None, None)), w_in, self.mixer_norm.weight, eps, h)
+        y = self._as_f32(self.mixer.forward(ctx, h, slot))
+        if self.ffn is None:
+            return (y, mix, w_out)
+        w_in2, mix2, w_out2 = self.hc[1]
+        h = torch.empty((T, d), dtype=ctx.act_dtype, device=x.device)
+        L.hyper_step(x, y, mix, w_out, w_in2, self.ffn_norm.weight, self.ffn_norm.spec.eps, h)
+        y = self._as_f32(self.ffn.forward(ctx, h))
+        return (y, mix2, w_out2)
+
+    @staticmethod
+    def flush(x, pending) -> None:
+        """Apply a pending update to the streams."""
+        from ..kernels import layer_ops as L
+        if pending is not None:
+            L.hyper_step(x, pending[0], pending[1], pending[2], None, None, 0.0, None)

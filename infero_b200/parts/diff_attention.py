@@ -37,6 +37,8 @@ class DiffAttention(Mixer):
         self.rope = None
         if spec.position is not None and spec.position.rotary_dim > 0:
             self.rope = part_class("position", spec.position.kind)(spec.position)
+            if getattr(self.rope, "amplitude", 1.0) != 1.0:
+                raise ValueError("this mixer's rotary kernel has no amplitude; the position table needs one")
             if getattr(self.rope, "pairing", None) != "adjacent":
                 raise ValueError("differential attention turns adjacent pairs; position kind "
                                  f"'{spec.position.kind}' pairs otherwise")

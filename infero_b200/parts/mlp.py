@@ -55,3 +55,45 @@ class SwiGluMlp(FeedForward):
         if not self.gate_up.forward_swiglu(h, act):
             K.swiglu(self.gate_up.forward(h, defer=True), act)
         return self.down.forward(act, defer=True, residual=True)
+
+
+class GluMlp(SwiGluMlp):
+    """delta = down(glu(gate(h), up(h))) with one of the gated activations of the kernels (``activation`` "swiglu" or
+    "glu_clamped" with ``limit`` and ``act_alpha``); the stacked layout of ``SwiGluMlp``.  The plain SwiGLU case keeps
+    the base class's fused epilogue; the others run the product and then the activation kernel."""
+
+    def forward(self, ctx, h):
+        s = self.spec
+        if s.activation == "swiglu":
+            return super().forward(ctx, h)
+        from ..kernels import layer_ops as L
+        act = torch.empty((h.shape[0], s.intermediate), dtype=h.dtype, device=h.device)
+        L.glu_act(self.gate_up.forward(h, defer=True), act, (s.activation, s.limit, s.act_alpha))
+        return self.down.forward(act, defer=True, residual=True)
+
+
+class Relu2Mlp(FeedForward):
+    """delta = down(relu(up(h))^2)."""
+
+    def __init__(self, spec: FeedForwardSpec, prefix: str):
+        self.spec, self.prefix = spec, prefix
+        self.names = spec.tensor_names()
+        self.up: Linear = None
+        self.down: Linear = None
+
+    def _n(self, role: str) -> str:
+        return f"{self.prefix}.{self.names[role]}{self.spec.weight_suffix}"
+
+    def declare(self) -> List[TensorDecl]:
+        d, ff = self.spec.hidden, self.spec.intermediate
+        return [TensorDecl(self._n("up"), (ff, d)), TensorDecl(self._n("down"), (d, ff))]
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.up = Linear(tensors[self._n("up")], None, self._n("up"))
+        self.down = Linear(tensors[self._n("down")], None, self._n("down"))
+
+    def forward(self, ctx, h):
+        from ..kernels import layer_ops as L
+        act = torch.empty((h.shape[0], self.spec.intermediate), dtype=h.dtype, device=h.device)
+        L.relu2(self.up.forward(h, defer=True), act)
+        return self.down.forward(act, defer=True, residual=True)

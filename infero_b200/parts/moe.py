@@ -89,3 +89,73 @@ class MoeSwiGlu(FeedForward):
         from ..kernels import moe as M
         M.experts(h, self.gate_up, self.down, idx, w, shared, gate, y)
         return y
+
+
+class GroupedMoe(FeedForward):
+    """Experts of the gated form down(glu(gate h, up h)) (the spec's ``activation``, ``limit``, ``act_alpha``), routed
+    by a softmax over all experts: z = Wr h in 32-bit, s = softmax(z); the ``top`` experts with the largest
+    s + correction are picked among the ``route_keep`` best of ``route_groups`` groups of neighbouring experts;
+    delta = sum_c s_c / (sum of the picked s + 1e-20) * expert_c(h).  A shared expert of the same form
+    (``shared_intermediate``, ``shared_limit``) runs for every token and is added as it is.
+
+    The experts' matrices are stacked as in ``MoeSwiGlu`` ([E, 2 ff, d] with rows alternating gate_j, up_j; [E, d, ff])
+    and run through the same three expert kernels."""
+
+    def __init__(self, spec: FeedForwardSpec, prefix: str):
+        from .mlp import GluMlp
+        self.spec, self.prefix = spec, prefix
+        self.E, self.top, self.ff = int(spec.experts), int(spec.top), int(spec.intermediate)
+        self.names = spec.tensor_names()
+        self.act = None if spec.activation == "swiglu" else (spec.activation, float(spec.limit), float(spec.act_alpha))
+        self.shared: Optional[SwiGluMlp] = None
+        if spec.shared_intermediate > 0:
+            sh = self.names["shared"]
+            sub = FeedForwardSpec(kind="glu", hidden=spec.hidden, intermediate=spec.shared_intermediate,
+                                  activation=spec.activation, limit=spec.shared_limit, act_alpha=spec.act_alpha,
+                                  names=tuple((r, f"{sh}.{self.names[r]}") for r in ("gate", "up", "down")),
+                                  weight_suffix=spec.weight_suffix)
+            self.shared = GluMlp(sub, prefix)
+
+    _expert = MoeSwiGlu._expert
+    _n = MoeSwiGlu._n
+
+    def declare(self) -> List[TensorDecl]:
+        d, ff = self.spec.hidden, self.ff
+        out: List[TensorDecl] = []
+        for e in range(self.E):
+            out += [TensorDecl(self._expert(e, "gate"), (ff, d)), TensorDecl(self._expert(e, "up"), (ff, d)),
+                    TensorDecl(self._expert(e, "down"), (d, ff))]
+        out.append(TensorDecl(self._n("router"), (self.E, d)))
+        if self.spec.route_correction:
+            out.append(TensorDecl(f"{self.prefix}.{self.names['correction']}", (self.E,), role="bias"))
+        if self.shared is not None:
+            out += self.shared.declare()
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        g = torch.stack([tensors[self._expert(e, "gate")] for e in range(self.E)])
+        u = torch.stack([tensors[self._expert(e, "up")] for e in range(self.E)])
+        self.gate_up = torch.stack([g, u], dim=2).reshape(self.E, 2 * self.ff, self.spec.hidden).contiguous()
+        self.down = torch.stack([tensors[self._expert(e, "down")] for e in range(self.E)]).contiguous()
+        self.route = Linear(tensors[self._n("router")], None, f"{self.prefix}.route")
+        self.correction = None
+        if self.spec.route_correction:
+            self.correction = tensors[f"{self.prefix}.{self.names['correction']}"].float().contiguous()
+        if self.shared is not None:
+            self.shared.bind(tensors)
+
+    def forward(self, ctx, h):
+        T, d = h.shape
+        z = self.route.forward(h, out_dtype=torch.float32)
+        idx, w = L.moe_select_grouped(z, self.correction, self.E, self.top, self.spec.route_groups, self.spec.route_keep)
+        shared = None
+        if self.shared is not None:
+            shared = self.shared.forward(ctx, h)
+            if isinstance(shared, K.Partials):
+                shared = shared.materialize(torch.float32)
+            elif shared.dtype != torch.float32:
+                shared = shared.float()
+        y = torch.empty((T, d), dtype=torch.float32, device=h.device)
+        from ..kernels import moe as M
+        M.experts(h, self.gate_up, self.down, idx, w, shared, None, y, self.act)
+        return y

@@ -47,3 +47,31 @@ class ScalarRmsNorm(RmsNorm):
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.scalar = tensors[self.weight_name].reshape(1).float().contiguous()
         self.weight = self.scalar.expand(self.spec.dim).contiguous()
+
+
+class LayerNorm(Norm):
+    """h = (v - mean(v)) * rsqrt(mean((v - mean(v))^2) + eps) * w with v = x (+ delta), no bias, all in 32-bit."""
+
+    def __init__(self, spec: NormSpec, weight_name: str):
+        self.spec = spec
+        self.weight_name = weight_name
+        self.weight: Optional[torch.Tensor] = None
+
+    def declare(self) -> List[TensorDecl]:
+        return [TensorDecl(self.weight_name, (self.spec.dim,), role="norm", init="ones")]
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.weight_name].float().contiguous()
+
+    def forward(self, ctx, x, delta, rows=None):
+        from ..kernels import layer_ops as L
+        n = x.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.spec.dim), dtype=ctx.act_dtype, device=x.device)
+        if hasattr(delta, "as_partials"):
+            delta = delta.as_partials()
+        if isinstance(delta, K.Partials):
+            delta = delta.materialize(torch.float32)
+        elif delta is not None and delta.dtype != torch.float32:
+            delta = delta.float()
+        L.add_layernorm(x, delta, self.weight, self.spec.eps, out, rows)
+        return out

@@ -91,6 +91,8 @@ def _register_builtin() -> None:
                           lambda c: c.to_model_spec(), model_types=("qwen2",))
     from .config.vufizen import VufizenConfig
     register_architecture("Vufizen", VufizenConfig.from_dict, lambda c: c.to_model_spec())
+    from .config.gositar import GositarConfig
+    register_architecture("Gositar", GositarConfig.from_dict, lambda c: c.to_model_spec())
 
 
 _register_builtin()
