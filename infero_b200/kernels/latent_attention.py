@@ -50,7 +50,9 @@ def _tile_heads(H: int, rows: int, device) -> torch.Tensor:
     t = _TILE_HEAD.get(key)
     if t is None:
         per = rows // TILE
-        t = torch.tensor([m // per for m in range(H * per)] + [H * rows], dtype=torch.int32, device=device)
+        # (made by device operations: a step that is being captured into a graph may meet a new size)
+        t = torch.cat([torch.arange(H * per, dtype=torch.int32, device=device) // per,
+                       torch.full((1,), H * rows, dtype=torch.int32, device=device)])
         if len(_TILE_HEAD) > 256:
             _TILE_HEAD.clear()
         _TILE_HEAD[key] = t

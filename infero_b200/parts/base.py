@@ -32,7 +32,7 @@ class TensorDecl:
     name: str
     shape: Tuple[int, ...]
     role: str = "matrix"          # matrix | embedding | norm | bias
-    init: str = "normal"          # normal | ones | uniform | conv  (random-weights mode)
+    init: str = "normal"          # normal | ones | uniform | conv | eye  (random-weights mode)
     optional: bool = False
 
 

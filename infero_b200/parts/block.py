@@ -212,7 +212,7 @@ class HyperPreNormBlock(Part):
         S = self.S
         for n in self._hc_names():
             out += [TensorDecl(f"{n}.in", (S,), role="bias", init="ones"), TensorDecl(f"{n}.out", (S,), role="bias", init="ones"),
-                    TensorDecl(f"{n}.mix", (S, S), role="bias")]
+                    TensorDecl(f"{n}.mix", (S, S), role="bias", init="eye")]
         return out
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:

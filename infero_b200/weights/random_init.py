@@ -32,6 +32,9 @@ def random_tensor(decl: TensorDecl, seed: int, dtype: torch.dtype, std: float = 
         t = torch.ones(decl.shape, dtype=torch.float32, device=device)
         if norm_std > 0:
             t += torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device) * norm_std
+    elif decl.init == "eye":                  # a square mixing matrix near the identity
+        t = torch.eye(decl.shape[0], dtype=torch.float32, device=device)
+        t += torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device) * max(norm_std, 0.05)
     elif decl.init == "uniform":              # numbers in [0, 1): lower bounds of gates and the like
         t = torch.rand(decl.shape, generator=g, dtype=torch.float32, device=device)
     elif decl.init == "conv":                 # taps of a short convolution: of the order of 1 / taps
