@@ -287,11 +287,14 @@ def main(argv=None) -> int:
                     help="instead of the headline workload: Vufizen beside Qwen2 at equal layer sizes, prompt and decode "
                          "steps and the kernels alone (infero_b200/tools/design_bench.py; its own JSON line)")
     ap.add_argument("--design-sizes", default="s,m")
+    ap.add_argument("--design", default="vufizen", choices=["vufizen", "gositar"],
+                    help="with --designs: which of the added designs runs beside Qwen2")
     args = ap.parse_args(argv)
 
     if args.designs and args.impl != "reference":
         from infero_b200.tools import design_bench
-        return design_bench.main(["--sizes", args.design_sizes, "--batch", str(args.batch), "--prompt", str(args.prefill_tokens)])
+        return design_bench.main(["--design", args.design, "--sizes", args.design_sizes, "--batch", str(args.batch),
+                                  "--prompt", str(args.prefill_tokens)])
     if args.impl == "reference":
         print(json.dumps({"impl": "reference",
                           "unavailable": "jackwangfeng/infero is a Rust workspace (no setup.py / pyproject.toml; "

@@ -14,7 +14,8 @@
 
 namespace {
 
-constexpr int THREADS = 256;
+constexpr int THREADS = 256;          // per token in steps of many tokens
+constexpr int THREADS_FEW = 1024;     // in steps of few tokens, where a block's own latency is what counts
 constexpr int MAX_STREAMS = 8;
 
 // the row v[0..d) in shared memory -> out = layer norm(v) * w
@@ -34,7 +35,7 @@ __device__ __forceinline__ void layernorm_row(const float* v, const float* __res
 }
 
 template <typename OutT>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS_FEW)
 add_layernorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ w, float eps,
                      OutT* __restrict__ out, const int* __restrict__ rows, int d) {
     extern __shared__ float row[];
@@ -54,7 +55,7 @@ add_layernorm_kernel(float* __restrict__ x, const float* __restrict__ delta, con
 }
 
 template <typename OutT>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS_FEW)
 hyper_step_kernel(float* __restrict__ xs, const float* __restrict__ y, int y_stride, const float* __restrict__ mix,
                   const float* __restrict__ w_out, const float* __restrict__ w_in, const float* __restrict__ norm_w,
                   float eps, OutT* __restrict__ h_out, float* __restrict__ u_out, const int* __restrict__ rows, int S, int d) {
@@ -124,10 +125,11 @@ int infero_add_layernorm(float* x, const float* delta, const float* w, float eps
     if (n == 0) return 0;
     const size_t sh = (size_t)d * sizeof(float);
     INFERO_REQUIRE(d >= 1 && sh <= 48 * 1024, "layer norm: width %d outside 1..12288", d);
+    const int threads = n <= 64 && d > THREADS ? THREADS_FEW : THREADS;
     if (out_dtype == INFERO_F32)
-        add_layernorm_kernel<float><<<n, THREADS, sh, stream>>>(x, delta, w, eps, (float*)out, rows, d);
+        add_layernorm_kernel<float><<<n, threads, sh, stream>>>(x, delta, w, eps, (float*)out, rows, d);
     else
-        add_layernorm_kernel<bf16><<<n, THREADS, sh, stream>>>(x, delta, w, eps, (bf16*)out, rows, d);
+        add_layernorm_kernel<bf16><<<n, threads, sh, stream>>>(x, delta, w, eps, (bf16*)out, rows, d);
     return infero_check_launch("add_layernorm");
 }
 
@@ -143,11 +145,12 @@ int infero_hyper_step(float* xs, const float* y, int y_stride, const float* mix,
     INFERO_REQUIRE(d >= 1 && sh <= 48 * 1024, "hyper-connections: width %d outside 1..12288", d);
     INFERO_REQUIRE(!y || (mix && w_out), "hyper-connections: an update needs its mix matrix and output weights");
     INFERO_REQUIRE(!norm_w || h_out, "hyper-connections: a norm needs somewhere to write");
+    const int threads = n <= 64 && d > THREADS ? THREADS_FEW : THREADS;
     if (h_dtype == INFERO_F32)
-        hyper_step_kernel<float><<<n, THREADS, sh, stream>>>(xs, y, y_stride, mix, w_out, w_in, norm_w, eps, (float*)h_out,
+        hyper_step_kernel<float><<<n, threads, sh, stream>>>(xs, y, y_stride, mix, w_out, w_in, norm_w, eps, (float*)h_out,
                                                            u_out, rows, S, d);
     else
-        hyper_step_kernel<bf16><<<n, THREADS, sh, stream>>>(xs, y, y_stride, mix, w_out, w_in, norm_w, eps, (bf16*)h_out,
+        hyper_step_kernel<bf16><<<n, threads, sh, stream>>>(xs, y, y_stride, mix, w_out, w_in, norm_w, eps, (bf16*)h_out,
                                                           u_out, rows, S, d);
     return infero_check_launch("hyper_step");
 }

@@ -10,7 +10,7 @@
 // Wuv -> finish (optional sigmoid gate per head, heads side by side).  The per-head products are the engine's
 // matrix-product kernels; queries and results are kept head-major, [H, rows, width], for them.
 //
-// prepare: one block per token.  c = row[:C] / sqrt(mean(row[:C]^2) + eps) * w (32-bit); the first `rot` of the R
+// prepare: per token one block for the latent row and one per group of heads.  c = row[:C] / sqrt(mean(row[:C]^2) + eps) * w (32-bit); the first `rot` of the R
 //   rotated coordinates of the key part and of every head's query turn by position * freq[i], cos and sin times
 //   `amp` (frequency table and amplitude come from the host, so any scaling of the frequencies is the host's);
 //   pairing 0: coordinate i with i + rot/2, pairing 1: 2i with 2i + 1.  The row [c | key part] goes to the token's
@@ -53,12 +53,14 @@ latent_prepare_kernel(const float* __restrict__ proj, int proj_stride, int q_off
                       float amp, const int* __restrict__ positions, const int* __restrict__ tok_entry,
                       const int* __restrict__ block_table, int max_blocks, int page_size, T* __restrict__ cache,
                       int write_cache, T* __restrict__ q_plain, float* __restrict__ q_rot, long long head_rows,
-                      int H, int D, int R, int C) {
+                      int H, int D, int R, int C, int heads_per_block) {
     __shared__ float red[32];
     const int t = blockIdx.x;
     const float* row = proj + (size_t)t * proj_stride;
     const float pos = (float)positions[t];
-    if (write_cache) {
+    if (blockIdx.y == 0) {
+        // the latent row
+        if (!write_cache) return;
         const float* kv = row + kv_off;
         float sq = 0.f;
         for (int i = threadIdx.x; i < C; i += blockDim.x) sq = fmaf(kv[i], kv[i], sq);
@@ -68,13 +70,16 @@ latent_prepare_kernel(const float* __restrict__ proj, int proj_stride, int q_off
         T* dst = cache + ((size_t)page * page_size + (p % page_size)) * (C + R);
         for (int i = threadIdx.x; i < C; i += blockDim.x) dst[i] = from_f32<T>(kv[i] * rstd * norm_w[i]);
         for (int i = threadIdx.x; i < R; i += blockDim.x) dst[C + i] = from_f32<T>(rotated(kv + C, i, rot, pairing, pos, freq, amp));
+        return;
     }
+    // the queries of heads [n0, n1)
+    const int n0 = (blockIdx.y - 1) * heads_per_block, n1 = min(H, n0 + heads_per_block);
     const float* q = row + q_off;
-    for (int i = threadIdx.x; i < H * D; i += blockDim.x) {
+    for (int i = n0 * D + threadIdx.x; i < n1 * D; i += blockDim.x) {
         const int n = i / D, c = i % D;
         q_plain[((size_t)n * head_rows + t) * D + c] = from_f32<T>(q[(size_t)n * (D + R) + c]);
     }
-    for (int i = threadIdx.x; i < H * R; i += blockDim.x) {
+    for (int i = n0 * R + threadIdx.x; i < n1 * R; i += blockDim.x) {
         const int n = i / R, c = i % R;
         q_rot[((size_t)n * head_rows + t) * R + c] = rotated(q + (size_t)n * (D + R) + D, c, rot, pairing, pos, freq, amp);
     }
@@ -176,14 +181,18 @@ int infero_latent_prepare(const float* proj, int proj_stride, int q_off, int kv_
     if (n_tokens == 0) return 0;
     INFERO_REQUIRE(rot >= 0 && rot <= R && rot % 2 == 0, "latent attention: %d rotated coordinates of %d", rot, R);
     INFERO_REQUIRE(head_rows >= n_tokens, "latent attention: %lld rows per head for %d tokens", head_rows, n_tokens);
+    // one block for a token's latent row, and one per group of heads (all heads in one block where tokens alone fill
+    // the multiprocessors)
+    const int heads_per_block = n_tokens >= 512 ? H : max(1, H / 8);
+    const dim3 grid(n_tokens, 1 + (H + heads_per_block - 1) / heads_per_block);
     if (dtype == INFERO_F32)
-        latent_prepare_kernel<float><<<n_tokens, PREP_THREADS, 0, stream>>>(proj, proj_stride, q_off, kv_off, norm_w, eps, freq,
+        latent_prepare_kernel<float><<<grid, PREP_THREADS, 0, stream>>>(proj, proj_stride, q_off, kv_off, norm_w, eps, freq,
             rot, pairing, amp, positions, tok_entry, block_table, max_blocks, page_size, (float*)cache, write_cache,
-            (float*)q_plain, q_rot, head_rows, H, D, R, C);
+            (float*)q_plain, q_rot, head_rows, H, D, R, C, heads_per_block);
     else
-        latent_prepare_kernel<bf16><<<n_tokens, PREP_THREADS, 0, stream>>>(proj, proj_stride, q_off, kv_off, norm_w, eps, freq,
+        latent_prepare_kernel<bf16><<<grid, PREP_THREADS, 0, stream>>>(proj, proj_stride, q_off, kv_off, norm_w, eps, freq,
             rot, pairing, amp, positions, tok_entry, block_table, max_blocks, page_size, (bf16*)cache, write_cache,
-            (bf16*)q_plain, q_rot, head_rows, H, D, R, C);
+            (bf16*)q_plain, q_rot, head_rows, H, D, R, C, heads_per_block);
     return infero_check_launch("latent_prepare");
 }
 

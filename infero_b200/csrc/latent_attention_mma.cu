@@ -56,17 +56,20 @@ latent_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_r
     const int k_hi = min(pos_first + n_tq, splits > 1 ? k_lo + chunk : 0x7fffffff);     // one past the last key
     const int* table = block_table + (size_t)e * max_blocks;
 
+    // a tile row is fetched by NT / KT threads: one look-up of its page, then its 16-byte chunks back to back
     auto load_tile = [&](int stage, int key0) {
-        bf16* dst = k_s + (size_t)stage * KT * LD;
+        constexpr int PER_ROW = NT / KT;
+        const int r = tid / PER_ROW, c0 = tid % PER_ROW;
+        const int j = key0 + r;
+        bf16* d = k_s + ((size_t)stage * KT + r) * LD;
         const int CH = W / 8;
-        for (int i = tid; i < KT * CH; i += NT) {
-            const int r = i / CH, c = i - r * CH;
-            const int j = key0 + r;
-            bf16* d = dst + (size_t)r * LD + c * 8;
-            int page = -1;
-            if (j >= k_lo && j < k_hi) page = table[j / page_size];
-            if (page >= 0) cp_async16(smem_addr(d), cache + ((size_t)page * page_size + (j % page_size)) * W + c * 8);
-            else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+        int page = -1;
+        if (j >= k_lo && j < k_hi) page = table[j / page_size];
+        if (page >= 0) {
+            const bf16* src = cache + ((size_t)page * page_size + (j % page_size)) * W;
+            for (int c = c0; c < CH; c += PER_ROW) cp_async16(smem_addr(d + c * 8), src + c * 8);
+        } else {
+            for (int c = c0; c < CH; c += PER_ROW) *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0, 0, 0, 0);
         }
     };
     const int key_begin = (k_lo / KT) * KT;
@@ -77,15 +80,21 @@ latent_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_r
         cp_async_commit();
     }
     // ---- queries: float32 -> bf16 rows [latent part | rotated part]; rows without a token or head are zero -------
-    for (int i = tid; i < ROWS * W; i += NT) {
-        const int r = i / W, c = i - r * W;
-        const int tq = r / HC, n = head0 + r % HC;
-        float v = 0.f;
-        if (tq < n_tq && n < H) {
-            const size_t row = (size_t)n * head_rows + tok0 + tq;
-            v = c < C ? q_lat[row * C + c] : q_rot[row * R + (c - C)];
+    // (four values per load, several loads in flight: a row's parts are multiples of 16 wide)
+    {
+        const int W4 = W / 4, C4 = C / 4;
+#pragma unroll 8
+        for (int i = tid; i < ROWS * W4; i += NT) {
+            const int r = i / W4, c = i - r * W4;
+            const int tq = r / HC, n = head0 + r % HC;
+            const bool live = tq < n_tq && n < H;
+            const size_t row = live ? (size_t)n * head_rows + tok0 + tq : 0;
+            const float4* src = c < C4 ? reinterpret_cast<const float4*>(q_lat + row * C) + c
+                                       : reinterpret_cast<const float4*>(q_rot + row * R) + (c - C4);
+            float4 v = __ldg(src);
+            if (!live) v = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<uint2*>(q_s + (size_t)r * LD + c * 4) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
         }
-        q_s[(size_t)r * LD + c] = __float2bfloat16_rn(v);
     }
 
     float o[NO][4];
@@ -211,25 +220,44 @@ latent_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_r
     }
 }
 
-// out[n, t, :] = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s, M = max_s m_s; one block per (token, head).
-__global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
-                                    long long head_rows, int H, int C, int splits) {
+// out[n, t, :] = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s, M = max_s m_s; one block per (token, head).  The
+// ranges' weights are worked out once into shared memory; every range left a finite result (zeros where it saw no key),
+// so the sums run over all of them without branches, several loads in flight, always in ascending order.
+constexpr int MAX_SPLITS = 64;
+__global__ void __launch_bounds__(256)
+latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
+                    long long head_rows, int H, int C, int splits) {
+    __shared__ float w_s[MAX_SPLITS];
+    __shared__ float inv_s;
     const int t = blockIdx.x / H, n = blockIdx.x % H;
     const size_t item0 = ((size_t)t * H + n) * splits;
-    float M = -CUDART_INF_F;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(item0 + s) * 2]);
-    float L = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float ms = part_ml[(item0 + s) * 2];
-        if (ms != -CUDART_INF_F) L += exp2f(ms - M) * part_ml[(item0 + s) * 2 + 1];
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float m0 = lane < splits ? part_ml[(item0 + lane) * 2] : -CUDART_INF_F;
+        float m1 = lane + 32 < splits ? part_ml[(item0 + lane + 32) * 2] : -CUDART_INF_F;
+        const float l0 = lane < splits ? part_ml[(item0 + lane) * 2 + 1] : 0.f;
+        const float l1 = lane + 32 < splits ? part_ml[(item0 + lane + 32) * 2 + 1] : 0.f;
+        const float M = warp_max(fmaxf(m0, m1));
+        const float w0 = m0 == -CUDART_INF_F ? 0.f : exp2f(m0 - M), w1 = m1 == -CUDART_INF_F ? 0.f : exp2f(m1 - M);
+        w_s[lane] = w0, w_s[lane + 32] = w1;
+        // (the sum in a fixed order: lane by lane through the shuffle tree)
+        const float L = warp_sum(w0 * l0 + w1 * l1);
+        if (lane == 0) inv_s = 1.0f / L;
     }
-    const float inv = 1.0f / L;
+    __syncthreads();
+    const float inv = inv_s;
     for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const float* src = part_o + item0 * C + c;
         float acc = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = part_ml[(item0 + s) * 2];
-            if (ms != -CUDART_INF_F) acc = fmaf(exp2f(ms - M), part_o[(item0 + s) * C + c], acc);
+        int s = 0;
+        for (; s + 8 <= splits; s += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = src[(size_t)(s + u) * C];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc = fmaf(w_s[s + u], v[u], acc);
         }
+        for (; s < splits; ++s) acc = fmaf(w_s[s], src[(size_t)s * C], acc);
         out[((size_t)n * head_rows + t) * C + c] = __float2bfloat16_rn(acc * inv);
     }
 }
@@ -280,6 +308,7 @@ int infero_latent_attention_mma(const float* q_lat, const float* q_rot, long lon
                                 int chunk, int splits, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     INFERO_REQUIRE(infero_latent_mma_supported(C, R), "latent attention: no tensor-core instance for a latent of %d + %d", C, R);
+    INFERO_REQUIRE(splits <= MAX_SPLITS, "latent attention: %d ranges of keys, at most %d", splits, MAX_SPLITS);
     INFERO_REQUIRE(splits >= 1 && (splits == 1 || (single && chunk > 0 && chunk % KT == 0 && part_o && part_ml)),
                    "latent attention: %d splits of %d keys", splits, chunk);
     const int HC = infero_latent_mma_heads(H);
@@ -292,8 +321,8 @@ int infero_latent_attention_mma(const float* q_lat, const float* q_rot, long lon
                                     HC, H, R, page_size, scale, chunk, splits, stream)
 #define BY_ROWS(C_)                                  \
     do {                                             \
-        if (rowg == 1) GO(C_, 1, 3);                 \
-        else if (rowg == 2) GO(C_, 2, 3);            \
+        if (rowg == 1) GO(C_, 1, 2);                 \
+        else if (rowg == 2) GO(C_, 2, 2);            \
         else GO(C_, 4, 2);                           \
     } while (0)
     if (C == 64) BY_ROWS(64);
@@ -305,7 +334,7 @@ int infero_latent_attention_mma(const float* q_lat, const float* q_rot, long lon
     if (rc) return rc;
     if (splits > 1) {
         // the tokens of the leading single-token entries are the first rows of the step
-        latent_merge_kernel<<<n_tiles * H, 128, 0, stream>>>(part_o, part_ml, (bf16*)out, head_rows, H, C, splits);
+        latent_merge_kernel<<<n_tiles * H, C >= 256 ? 256 : 128, 0, stream>>>(part_o, part_ml, (bf16*)out, head_rows, H, C, splits);
     }
     return infero_check_launch("latent_attention_mma");
 }

@@ -14,7 +14,7 @@ import torch
 from . import _check, _i32, _ptr, _stream, lib
 
 ENABLED = os.environ.get("INFERO_LATENT_MMA", "1") != "0"
-MIN_CHUNK = 256            # fewest keys per range of a cut context
+MIN_CHUNK = int(os.environ.get("INFERO_LATENT_MIN_CHUNK", "64"))     # fewest keys per range of a cut context
 launches = {"single": 0, "tiled": 0, "cut": 0}      # how often each form ran (tests look at it)
 
 
@@ -24,7 +24,7 @@ def supported(C: int, R: int) -> bool:
 
 def plan_splits(n_tok: int, head_blocks: int, visible: int, sms: int):
     """(keys per range, ranges): about two CTAs per multiprocessor, ranges of whole key tiles, at least MIN_CHUNK keys."""
-    want = max(1, (2 * sms) // max(1, n_tok * head_blocks))
+    want = max(1, (int(os.environ.get("INFERO_LATENT_CTAS_PER_SM", "2")) * sms) // max(1, n_tok * head_blocks))
     splits = max(1, min(want, visible // MIN_CHUNK, 64))
     chunk = -(-visible // splits)
     chunk = -(-chunk // 32) * 32

@@ -1,13 +1,18 @@
-"""Vufizen beside Qwen2 at equal layer sizes: whole prompt steps and decode steps, and the designs' own kernels
-one by one against their rooflines.
+"""Vufizen or Gositar beside Qwen2 at equal layer sizes: whole prompt steps and decode steps, and the designs' own
+kernels one by one against their rooflines.
 
-    python -m infero_b200.tools.design_bench [--sizes s,m] [--prompt 2048] [--context 2048] [--batch 8] [--layers 8]
+    python -m infero_b200.tools.design_bench [--design vufizen|gositar] [--sizes s,m] [--prompt 2048] [--context 2048]
+                                             [--batch 8] [--layers 8]
 
 (also ``bench.py --designs``).  Random weights made on the device, bf16.  Per size two models of the same width
 and depth: Vufizen (HGRN2 and differential-attention layers alternating, routed experts with a shared one) and
 Qwen2 with the same head count, a head as wide as both maps together, and a feed-forward as wide as what one token
 uses of the experts.  Steps are timed with CUDA events after warm-up, an L2 flush between timed steps; kernels are
 timed alone the same way.  One JSON line at the end.
+
+Gositar (``--design gositar``): latent attention in every layer (both mixer types alternating), dense squared-relu and
+group-routed expert feed-forwards alternating, four residual streams; beside Qwen2 with the same head count, heads of
+128, a quarter as many kv heads, and a feed-forward as wide as what one token uses on average.
 """
 from __future__ import annotations
 
@@ -24,6 +29,38 @@ SIZES = {
     "m": dict(width=2048, heads=16, kv=4, dim=64, vdim=128, experts=32, top=4, ff=768, shared=1536, vocab=32000),
     "l": dict(width=4096, heads=32, kv=8, dim=64, vdim=128, experts=64, top=8, ff=768, shared=2048, vocab=32000),
 }
+
+
+GOSITAR_SIZES = {
+    "t": dict(width=256, heads=4, dim=32, rot=16, vdim=32, rank=64, experts=4, top=2, groups=(2, 1), ff=64, shared=128, dense=512,
+              streams=2, vocab=1000),                                                                         # for tests
+    "s": dict(width=1024, heads=8, dim=64, rot=32, vdim=64, rank=256, experts=16, top=4, groups=(4, 2), ff=512, shared=1024,
+              dense=4096, streams=4, vocab=32000),
+    "m": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, rank=512, experts=32, top=4, groups=(4, 2), ff=768, shared=1536,
+              dense=6144, streams=4, vocab=32000),
+    "l": dict(width=4096, heads=32, dim=128, rot=64, vdim=128, rank=512, experts=64, top=8, groups=(8, 4), ff=768, shared=2048,
+              dense=8192, streams=4, vocab=32000),
+}
+
+
+def gositar_config(z, layers):
+    mix = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["rank"],
+           "scale": (z["dim"] + z["rot"]) ** -0.5,
+           "rot": {"base": 10000.0, "dims": z["rot"], "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"], "limit": 7.0}, "shared": {"ff": z["shared"], "limit": 7.0},
+           "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}}
+    dense = {"kind": "dense", "ff": z["dense"]}
+    return {"architecture": "Gositar", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "streams": z["streams"],
+            "layers": [{"type": "latent_attention" if i % 2 == 0 else "latent_attention_2", "mixer": mix,
+                        "mlp": dense if i % 2 == 0 else moe} for i in range(layers)]}
+
+
+def qwen2_beside_gositar(z, layers):
+    used = (z["dense"] * 2 // 3 + z["top"] * z["ff"] + z["shared"]) // 2          # (two matrices of `dense` against three)
+    return {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": layers,
+            "hidden_size": z["width"], "num_attention_heads": z["heads"], "num_key_value_heads": max(1, z["heads"] // 4),
+            "head_dim": 128, "intermediate_size": -(-used // 64) * 64, "vocab_size": z["vocab"],
+            "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False}
 
 
 def vufizen_config(z, layers):
@@ -263,8 +300,145 @@ def time_kernels(z, T, context, batch, timer, peaks):
     return rows
 
 
+def time_gositar_kernels(z, T, context, batch, timer, peaks):
+    """Gositar's kernels alone, each beside the kernel of the built-in decoder that does the like job."""
+    import numpy as np
+    import torch
+    from infero_b200 import kernels as K
+    from infero_b200.kernels import attention as A, latent_attention as LA, layer_ops as L, moe as M, tc_gemm
+    from infero_b200.parts.linear import Linear
+    dev, bf = "cuda:0", torch.bfloat16
+    d, H, D, R, V, C, S = z["width"], z["heads"], z["dim"], z["rot"], z["vdim"], z["rank"], z["streams"]
+    E, top, ff = z["experts"], z["top"], z["ff"]
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *s, dtype=bf, k=1.0: (torch.randn(s, generator=g, device=dev) * k).to(dtype)     # noqa: E731
+    i32 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=dev)                 # noqa: E731
+    hbm, tfl = peaks["hbm_gbs"], peaks["bf16_tflops"]
+    rows = {}
+
+    def note(name, ms, bytes_=0.0, flops=0.0):
+        r = {"us": round(ms * 1e3, 1)}
+        if bytes_:
+            r["gb_s"] = round(bytes_ / ms / 1e6, 1)
+            r["hbm_frac"] = round(bytes_ / ms / 1e6 / hbm, 3)
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 1)
+            r["tensor_frac"] = round(flops / ms / 1e9 / tfl, 3)
+        rows[name] = r
+
+    def batch_ctx(q_lens, pos0, ps=16):
+        E_ = len(q_lens)
+        per = [-(-(p + n) // ps) for p, n in zip(pos0, q_lens)]
+        table = torch.full((E_, max(per)), -1, dtype=torch.int32)
+        at = 0
+        for e, n in enumerate(per):
+            table[e, :n] = torch.arange(at, at + n, dtype=torch.int32)
+            at += n
+        qs = np.concatenate([[0], np.cumsum(q_lens)[:-1]])
+        ctx = types.SimpleNamespace(
+            n_entries=E_, n_tokens=int(sum(q_lens)), h_q_len=np.asarray(q_lens, dtype=np.int32), h_pos0=np.asarray(pos0, dtype=np.int32),
+            tok_entry=i32(np.repeat(np.arange(E_), q_lens)), positions=i32(np.concatenate([p + np.arange(n) for p, n in zip(pos0, q_lens)])),
+            entry_q_start=i32(qs), entry_q_len=i32(q_lens), entry_pos0=i32(pos0), entry_slot=i32(np.arange(E_)), kv_bound=None)
+        return ctx, table.to(dev), at
+
+    G, Dq = max(1, H // 4), 128
+    for label, q_lens, pos0 in (("prefill", [T], [0]), ("decode", [1] * batch, [context - 1] * batch)):
+        ctx, table, pages = batch_ctx(q_lens, pos0)
+        n = ctx.n_tokens
+        pairs = T * T / 2 if label == "prefill" else batch * context           # (query, key) pairs per head
+        keys = T if label == "prefill" else batch * context
+        # ---- attention over the latent rows ------------------------------------------------------------------------
+        kv = types.SimpleNamespace(k=rnd(pages, 1, 16, C + R), v=None, page_size=16, group=0)
+        rows_h = -(-n // 128) * 128
+        q_lat, q_rot = rnd(H, rows_h, C, dtype=torch.float32), rnd(H, rows_h, R, dtype=torch.float32)
+        o_lat = torch.empty(H, rows_h, C, dtype=bf, device=dev)
+        ms = timer(lambda: LA.attention(ctx, q_lat, q_rot, o_lat, kv, table, n, H, C, R, (D + R) ** -0.5))
+        note(f"latent_attention_{label}", ms, 2.0 * (C + R) * keys + n * H * (4.0 * (C + R) + 2.0 * C), 2.0 * H * (2 * C + R) * pairs)
+        rows[f"latent_attention_{label}"]["unabsorbed_tflops"] = round(2.0 * H * (D + R + V) * pairs / ms / 1e9, 1)
+        # ---- the per-head products around it -----------------------------------------------------------------------
+        q_plain, up_k = rnd(H, rows_h, D), rnd(H, C, D, k=0.05)
+        ms = timer(lambda: LA.per_head_product(q_plain, up_k, q_lat, n))
+        note(f"per_head_up_k_{label}", ms, 2.0 * H * C * D + H * rows_h * (2.0 * D + 4.0 * C), 2.0 * H * rows_h * C * D)
+        up_v, val = rnd(H, V, C, k=0.05), torch.empty(H, rows_h, V, dtype=torch.float32, device=dev)
+        ms = timer(lambda: LA.per_head_product(o_lat, up_v, val, n))
+        note(f"per_head_up_v_{label}", ms, 2.0 * H * C * V + H * rows_h * (2.0 * C + 4.0 * V), 2.0 * H * rows_h * C * V)
+        # ---- prepare beside rotary + cache append --------------------------------------------------------------------
+        width = H * (D + R) + C + R + H
+        proj, nw, fr = rnd(n, width, dtype=torch.float32), torch.ones(C, device=dev), torch.rand(R // 2, device=dev)
+        ms = timer(lambda: LA.prepare(proj, 0, H * (D + R), nw, 1e-5, fr, "adjacent", 1.2, ctx.positions, ctx.tok_entry, table, kv.k,
+                                      16, q_plain, q_rot, n, H, D, R, C))
+        note(f"latent_prepare_{label}", ms, n * (4.0 * width + 2.0 * (C + R) + H * (2.0 * D + 4.0 * R)))
+        gate, attn = proj[:, width - H:], torch.empty(n, H * V, dtype=bf, device=dev)
+        ms = timer(lambda: LA.finish(val, gate, attn, n, H, V))
+        note(f"latent_finish_{label}", ms, n * H * V * 6.0)
+        # ---- the built-in attention: heads of 128, a quarter as many kv heads ----------------------------------------
+        k2, v2 = rnd(pages, G, 16, Dq), rnd(pages, G, 16, Dq)
+        q2, out2 = rnd(n, H * Dq), torch.empty(n, H * Dq, dtype=bf, device=dev)
+        ms = timer(lambda: A.attention_any(q2, out2, k2, v2, table, ctx.tok_entry, ctx.positions, H, G, Dq, 16, None, Dq ** -0.5,
+                                           ctx.h_q_len, ctx.h_pos0, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_pos0))
+        note(f"gqa_attention_{label}", ms, 2.0 * G * 2 * Dq * keys + 4.0 * n * H * Dq, 2.0 * H * 2 * Dq * pairs)
+        if label == "prefill":
+            ms = timer(lambda: A.prefill(q2, out2, k2, v2, table, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_pos0, 1, 0,
+                                         -(-T // 64), H, G, Dq, 16, None, Dq ** -0.5))
+            note("gqa_attention_prefill_mma_sync", ms, 2.0 * G * 2 * Dq * keys + 4.0 * n * H * Dq, 2.0 * H * 2 * Dq * pairs)
+        qkv = rnd(n, (H + 2 * G) * Dq)
+        inv2 = torch.rand(Dq // 2, device=dev)
+        ms = timer(lambda: K.rope_cache(qkv, ctx.positions, ctx.tok_entry, table, inv2, k2, v2, H, G, Dq, 16))
+        note(f"rope_cache_{label}", ms, n * (H + 2 * G) * Dq * 2 * 2)
+
+    # ---- feed-forward: group-routed experts with the clamped activation beside a dense SwiGLU of the width one token uses ----
+    gu, dn = rnd(E, 2 * ff, d, k=0.05), rnd(E, d, ff, k=0.05)
+    router, corr = rnd(E, d, k=0.1), rnd(E, dtype=torch.float32, k=0.1)
+    dense_ff = top * ff
+    wgu, wdn = rnd(2 * dense_ff, d, k=0.05), rnd(d, dense_ff, k=0.05)
+    wup, wdown = rnd(z["dense"], d, k=0.05), rnd(d, z["dense"], k=0.05)
+    act3 = ("glu_clamped", 7.0, 1.702)
+    for label, n in (("prefill", T), ("decode", batch)):
+        h = rnd(n, d)
+        y = torch.empty(n, d, device=dev)
+        route = Linear(router)
+        idx, w = L.moe_select_grouped(route.forward(h, out_dtype=torch.float32), corr, E, top, *z["groups"])
+        ms = timer(lambda: L.moe_select_grouped(route.forward(h, out_dtype=torch.float32), corr, E, top, *z["groups"]))
+        note(f"moe_route_grouped_{label}", ms, 2.0 * (n * d + E * d))
+        used = min(E, n * top)
+        ms = timer(lambda: M.experts(h, gu, dn, idx, w, None, None, y, act3))
+        note(f"moe_experts_clamped_{label}", ms, 2.0 * used * 3 * ff * d + 2.0 * n * d + 4.0 * n * d, 6.0 * n * top * ff * d)
+        act = torch.empty(n, dense_ff, dtype=bf, device=dev)
+        o = torch.empty(n, d, dtype=torch.float32, device=dev)
+
+        def dense():
+            if not tc_gemm.gemm_swiglu(h, wgu, act):
+                K.swiglu(K.Partials(tc_gemm.partials(h, wgu)), act)
+            tc_gemm.gemm(act, wdn, None, o)
+        ms = timer(dense)
+        note(f"dense_swiglu_{label}", ms, 2.0 * 3 * dense_ff * d + 6.0 * n * d, 6.0 * n * dense_ff * d)
+        up, down = Linear(wup), Linear(wdown)
+        a2 = torch.empty(n, z["dense"], dtype=bf, device=dev)
+
+        def relu2():
+            L.relu2(up.forward(h, defer=True), a2)
+            r = down.forward(a2, defer=True, residual=True)
+            if isinstance(r, K.Partials):
+                r.materialize(torch.float32)
+        ms = timer(relu2)
+        note(f"dense_relu2_{label}", ms, 2.0 * 2 * z["dense"] * d + 6.0 * n * d, 4.0 * n * z["dense"] * d)
+
+    # ---- the residual: one pass over S streams beside add + RMSNorm over one -------------------------------------------
+    for label, n in (("prefill", T), ("decode", batch)):
+        xs, yv = rnd(n, S, d, dtype=torch.float32), rnd(n, d, dtype=torch.float32)
+        mix, wo, wi = rnd(S, S, dtype=torch.float32), rnd(S, dtype=torch.float32), rnd(S, dtype=torch.float32)
+        nw, hb = torch.ones(d, device=dev), torch.empty(n, d, dtype=bf, device=dev)
+        ms = timer(lambda: L.hyper_step(xs, yv, mix, wo, wi, nw, 1e-5, hb))
+        note(f"hyper_step_{label}", ms, n * d * (8.0 * S + 4 + 2))
+        x = rnd(n, d, dtype=torch.float32)
+        ms = timer(lambda: K.add_rmsnorm(x, yv, nw, 1e-5, hb))
+        note(f"add_rmsnorm_{label}", ms, n * d * (4 + 4 + 4 + 2))
+    return rows
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="design_bench")
+    ap.add_argument("--design", default="vufizen", choices=["vufizen", "gositar"])
     ap.add_argument("--sizes", default="s,m")
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--context", type=int, default=2048)
@@ -284,17 +458,20 @@ def main(argv=None) -> int:
     except (OSError, KeyError, ValueError):
         pass
     timer = _Timer()
-    out = {"bench": "designs", "dtype": "bf16", "data": "synthetic", "prompt": args.prompt, "context": args.context,
+    gositar = args.design == "gositar"
+    sizes, design_cfg, beside_cfg = (GOSITAR_SIZES, gositar_config, qwen2_beside_gositar) if gositar else (SIZES, vufizen_config, qwen2_config)
+    out = {"bench": "designs", "design": args.design, "dtype": "bf16", "data": "synthetic", "prompt": args.prompt, "context": args.context,
            "batch": args.batch, "layers": args.layers, "peaks": peaks, "sizes": {}}
     for name in [s for s in args.sizes.split(",") if s]:
-        z = SIZES[name]
+        z = sizes[name]
         out["sizes"][name] = {"shape": z,
-                              "vufizen": time_model(vufizen_config(z, args.layers), args.prompt, args.context, args.batch, timer),
-                              "qwen2": time_model(qwen2_config(z, args.layers), args.prompt, args.context, args.batch, timer)}
+                              args.design: time_model(design_cfg(z, args.layers), args.prompt, args.context, args.batch, timer),
+                              "qwen2": time_model(beside_cfg(z, args.layers), args.prompt, args.context, args.batch, timer)}
         print(f"[design_bench] {name}: {json.dumps(out['sizes'][name])}", file=sys.stderr, flush=True)
     if args.kernels_at:
+        each = time_gositar_kernels if gositar else time_kernels
         out["kernels"] = {"size": args.kernels_at,
-                          "rows": time_kernels(SIZES[args.kernels_at], args.prompt, args.context, args.batch, timer, peaks)}
+                          "rows": each(sizes[args.kernels_at], args.prompt, args.context, args.batch, timer, peaks)}
     print(json.dumps(out))
     return 0
 

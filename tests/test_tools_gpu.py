@@ -58,3 +58,19 @@ def test_design_bench_prints_both_designs_and_the_kernels(capsys):
     rows = line["kernels"]["rows"]
     assert {"diff_attention_prefill", "hgrn2_scan_prefill", "moe_experts_decode", "gated_norm_add_prefill"} <= set(rows)
     assert all(r["us"] > 0 for r in rows.values())
+
+
+def test_design_bench_of_gositar(capsys):
+    """``bench.py --designs --design gositar`` at a size made for tests."""
+    import json
+    from infero_b200.tools import design_bench
+    assert design_bench.main(["--design", "gositar", "--sizes", "t", "--prompt", "600", "--context", "300", "--batch", "3",
+                              "--layers", "2", "--kernels-at", "t"]) == 0
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert line["design"] == "gositar" and set(line["sizes"]["t"]) == {"shape", "gositar", "qwen2"}
+    for design in ("gositar", "qwen2"):
+        assert line["sizes"]["t"][design]["prefill_tok_s"] > 0 and line["sizes"]["t"][design]["decode_tok_s"] > 0
+    rows = line["kernels"]["rows"]
+    assert {"latent_attention_prefill", "latent_attention_decode", "moe_experts_clamped_decode", "hyper_step_prefill",
+            "per_head_up_k_prefill", "dense_relu2_decode"} <= set(rows)
+    assert all(r["us"] > 0 for r in rows.values())
