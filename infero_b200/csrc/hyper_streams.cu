@@ -56,7 +56,8 @@ add_layernorm_kernel(float* __restrict__ x, const float* __restrict__ delta, con
 
 template <typename OutT>
 __global__ void __launch_bounds__(THREADS_FEW)
-hyper_step_kernel(float* __restrict__ xs, const float* __restrict__ y, int y_stride, const float* __restrict__ mix,
+hyper_step_kernel(float* __restrict__ xs, const float* __restrict__ y, int y_stride, int y_splits, long long y_split_stride,
+                  const float* __restrict__ mix,
                   const float* __restrict__ w_out, const float* __restrict__ w_in, const float* __restrict__ norm_w,
                   float eps, OutT* __restrict__ h_out, float* __restrict__ u_out, const int* __restrict__ rows, int S, int d) {
     extern __shared__ float row[];
@@ -70,13 +71,14 @@ hyper_step_kernel(float* __restrict__ xs, const float* __restrict__ y, int y_str
     __syncthreads();
     const size_t t = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
     float* xt = xs + t * S * d;
-    const bool read_out = w_in || u_out;
+    const bool read_out = w_in || u_out || norm_w;       // (without w_in: the plain sum of the streams)
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float v[MAX_STREAMS];
 #pragma unroll
         for (int s = 0; s < MAX_STREAMS; ++s) v[s] = s < S ? xt[(size_t)s * d + i] : 0.f;
         if (y) {
-            const float yv = y[t * y_stride + i];
+            float yv = y[t * y_stride + i];
+            for (int k = 1; k < y_splits; ++k) yv += y[(size_t)k * y_split_stride + t * y_stride + i];     // ascending order
             float nv[MAX_STREAMS];
 #pragma unroll
             for (int r = 0; r < MAX_STREAMS; ++r) {
@@ -133,24 +135,28 @@ int infero_add_layernorm(float* x, const float* delta, const float* w, float eps
     return infero_check_launch("add_layernorm");
 }
 
-// xs float32 [T, S, d].  y (float32, row stride y_stride) with mix [S, S] (from, to) and w_out [S]: update the streams.
+// xs float32 [T, S, d].  y (float32, row stride y_stride; or y_splits partial sums of a product, y_split_stride elements
+// apart, added up here) with mix [S, S] (from, to) and w_out [S]: update the streams.
 // w_in [S] with norm_w [d]: h_out [n, d] = layer norm(sum_s w_in[s] xs[s]) * norm_w.  norm_w null: u_out float32 [n, d]
 // = sum_s w_in[s] xs[s] (w_in null: the plain sum).  rows (or null): the tokens to work on, n of them.
-int infero_hyper_step(float* xs, const float* y, int y_stride, const float* mix, const float* w_out, const float* w_in,
+int infero_hyper_step(float* xs, const float* y, int y_stride, int y_splits, long long y_split_stride, const float* mix,
+                      const float* w_out, const float* w_in,
                       const float* norm_w, float eps, void* h_out, int h_dtype, float* u_out, const int* rows, int n,
                       int S, int d, cudaStream_t stream) {
     if (n == 0) return 0;
     const size_t sh = (size_t)d * sizeof(float);
     INFERO_REQUIRE(S >= 1 && S <= MAX_STREAMS, "hyper-connections: %d streams outside 1..%d", S, MAX_STREAMS);
     INFERO_REQUIRE(d >= 1 && sh <= 48 * 1024, "hyper-connections: width %d outside 1..12288", d);
-    INFERO_REQUIRE(!y || (mix && w_out), "hyper-connections: an update needs its mix matrix and output weights");
+    INFERO_REQUIRE(!y || (mix && w_out && y_splits >= 1), "hyper-connections: an update needs its mix matrix and output weights");
     INFERO_REQUIRE(!norm_w || h_out, "hyper-connections: a norm needs somewhere to write");
     const int threads = n <= 64 && d > THREADS ? THREADS_FEW : THREADS;
     if (h_dtype == INFERO_F32)
-        hyper_step_kernel<float><<<n, threads, sh, stream>>>(xs, y, y_stride, mix, w_out, w_in, norm_w, eps, (float*)h_out,
+        hyper_step_kernel<float><<<n, threads, sh, stream>>>(xs, y, y_stride, y_splits, y_split_stride, mix, w_out, w_in, norm_w, eps,
+                                                           (float*)h_out,
                                                            u_out, rows, S, d);
     else
-        hyper_step_kernel<bf16><<<n, threads, sh, stream>>>(xs, y, y_stride, mix, w_out, w_in, norm_w, eps, (bf16*)h_out,
+        hyper_step_kernel<bf16><<<n, threads, sh, stream>>>(xs, y, y_stride, y_splits, y_split_stride, mix, w_out, w_in, norm_w, eps,
+                                                          (bf16*)h_out,
                                                           u_out, rows, S, d);
     return infero_check_launch("hyper_step");
 }

@@ -5,9 +5,10 @@
 // heads of one request (HC = 16, 32 or 64 heads; TQ = 1 for single tokens, 64 / HC in a prompt portion) and walks
 // the request's keys in tiles of 32, fetched once for all its rows by cp.async into a ring in shared memory.
 // Queries arrive as float32 (the plain parts already carried through Wuk^T) and are rounded to bf16 into shared
-// memory once; scores, running maximum and sum are 32-bit.  Two warps share 16 rows: both form the rows' scores
-// (the same numbers, instruction for instruction) and each owns one half of the C result columns, so the result
-// tile of 16 x C/2 stays in registers.  Key tiles start at multiples of 32 of the absolute position, so what is
+// memory once; scores, running maximum and sum are 32-bit.  Two warps share 16 rows: each forms the rows' scores
+// with 16 of a tile's 32 keys, they exchange the rows' maxima and their softmax weights (as tensor-core fragments,
+// whose layout is the same lane by lane) through shared memory, and each owns one half of the C result columns, so
+// the result tile of 16 x C/2 stays in registers.  Key tiles start at multiples of 32 of the absolute position, so what is
 // computed for a token does not depend on how its prompt was cut.
 //
 // Single tokens with long contexts are cut into `splits` ranges of keys, one CTA each; every CTA leaves its
@@ -19,6 +20,9 @@ namespace {
 using namespace attn;
 
 constexpr int KT = 32;                        // keys per tile
+
+// a barrier of the two warps that share 16 rows (barrier 0 is the block's)
+__device__ __forceinline__ void pair_sync(int rg) { asm volatile("bar.sync %0, 64;" ::"r"(rg + 1) : "memory"); }
 
 template <int C, int ROWG, int STAGES>
 __global__ void __launch_bounds__(ROWG * 64, 1)
@@ -35,6 +39,10 @@ latent_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_r
     bf16* k_s = q_s + ROWS * LD;                           // [STAGES][KT][LD]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rg = warp >> 1, half = warp & 1;
+    // what the two warps of 16 rows hand each other: row maxima (and, at the end, sums), and their softmax weights as
+    // tensor-core fragments
+    uint4* xp = reinterpret_cast<uint4*>(k_s + (size_t)STAGES * KT * LD) + rg * 64;          // [2][32]
+    float* xm = reinterpret_cast<float*>(reinterpret_cast<uint4*>(k_s + (size_t)STAGES * KT * LD) + ROWG * 64) + rg * 32;   // [2][16]
 
     // ---- which request, which of its tokens ---------------------------------------------------------------
     int e = entry_first, t0 = 0;
@@ -112,31 +120,29 @@ latent_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_r
         cp_async_commit();
         const bf16* kt_s = k_s + (size_t)(kt % STAGES) * KT * LD;
         const int key0 = key_begin + kt * KT;
-        // ---- s = q k^T: four n-tiles of 8 keys, W / 16 k-steps ------------------------------------------------
-        float s[4][4];
+        // ---- s = q k^T for this warp's 16 of the tile's 32 keys: two n-tiles of 8 keys, W / 16 k-steps -------------------
+        float s[2][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+        for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
         {
             const bf16* qa = q_s + (size_t)(rg * 16 + (lane & 7) + (mi & 1) * 8) * LD + (mi >> 1) * 8;
-            const bf16* kb = kt_s + (size_t)((mi >> 1) * 8 + (lane & 7)) * LD + (mi & 1) * 8;
+            const bf16* kb = kt_s + (size_t)(half * 16 + (mi >> 1) * 8 + (lane & 7)) * LD + (mi & 1) * 8;
+#pragma unroll 4
             for (int ks = 0; ks < W / 16; ++ks) {
                 uint32_t a[4], b[4];
                 ldmatrix_x4(a, smem_addr(qa + ks * 16));
                 ldmatrix_x4(b, smem_addr(kb + ks * 16));
                 mma16816(s[0], a, b[0], b[1]);
                 mma16816(s[1], a, b[2], b[3]);
-                ldmatrix_x4(b, smem_addr(kb + (size_t)16 * LD + ks * 16));
-                mma16816(s[2], a, b[0], b[1]);
-                mma16816(s[3], a, b[2], b[3]);
             }
         }
-        // ---- mask and statistics ----------------------------------------------------------------------------------
+        // ---- mask; the rows' maxima over all 32 keys, through the pair's exchange -------------------------------------
         float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
+        for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int x = 0; x < 2; ++x) {
-                const int j = key0 + nt * 8 + cq * 2 + x;
+                const int j = key0 + half * 16 + nt * 8 + cq * 2 + x;
                 const bool in = j >= k_lo && j < k_hi;
                 const float a = (in && j <= hi0) ? s[nt][x] * scale_log2 : -CUDART_INF_F;
                 const float b = (in && j <= hi1) ? s[nt][2 + x] * scale_log2 : -CUDART_INF_F;
@@ -147,30 +153,37 @@ latent_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_r
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        if (cq == 0) xm[half * 16 + g] = mx0, xm[half * 16 + g + 8] = mx1;
+        pair_sync(rg);
+        mx0 = fmaxf(mx0, xm[(half ^ 1) * 16 + g]);
+        mx1 = fmaxf(mx1, xm[(half ^ 1) * 16 + g + 8]);
         const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
         const float sub0 = mn0 == -CUDART_INF_F ? 0.f : mn0, sub1 = mn1 == -CUDART_INF_F ? 0.f : mn1;
         const float corr0 = exp2f(m[0] - sub0), corr1 = exp2f(m[1] - sub1);
         m[0] = mn0, m[1] = mn1;
         float sum0 = 0.f, sum1 = 0.f;
-        uint32_t pf[2][4];                                     // two k-steps of 16 keys
-#pragma unroll
-        for (int kk = 0; kk < 2; ++kk) {
+        uint32_t pf[2][4];                                     // two k-steps of 16 keys: this warp's and its partner's
+        {
             float p[2][4];
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
-                p[nt][0] = exp2f(s[kk * 2 + nt][0] - sub0);
-                p[nt][1] = exp2f(s[kk * 2 + nt][1] - sub0);
-                p[nt][2] = exp2f(s[kk * 2 + nt][2] - sub1);
-                p[nt][3] = exp2f(s[kk * 2 + nt][3] - sub1);
+                p[nt][0] = exp2f(s[nt][0] - sub0);
+                p[nt][1] = exp2f(s[nt][1] - sub0);
+                p[nt][2] = exp2f(s[nt][2] - sub1);
+                p[nt][3] = exp2f(s[nt][3] - sub1);
                 sum0 += p[nt][0] + p[nt][1];
                 sum1 += p[nt][2] + p[nt][3];
             }
-            pf[kk][0] = pack_bf16(p[0][0], p[0][1]);
-            pf[kk][1] = pack_bf16(p[0][2], p[0][3]);
-            pf[kk][2] = pack_bf16(p[1][0], p[1][1]);
-            pf[kk][3] = pack_bf16(p[1][2], p[1][3]);
+            const uint4 own = make_uint4(pack_bf16(p[0][0], p[0][1]), pack_bf16(p[0][2], p[0][3]), pack_bf16(p[1][0], p[1][1]),
+                                         pack_bf16(p[1][2], p[1][3]));
+            xp[half * 32 + lane] = own;                        // the fragment layout is the same in both warps, lane by lane
+            pair_sync(rg);
+            const uint4 other = xp[(half ^ 1) * 32 + lane];
+            const uint4 lo = half ? other : own, hi = half ? own : other;       // keys 0..15 and 16..31 of the tile
+            pf[0][0] = lo.x, pf[0][1] = lo.y, pf[0][2] = lo.z, pf[0][3] = lo.w;
+            pf[1][0] = hi.x, pf[1][1] = hi.y, pf[1][2] = hi.z, pf[1][3] = hi.w;
         }
-        l[0] = l[0] * corr0 + sum0;                            // per-thread partial sums; the quad is added up at the end
+        l[0] = l[0] * corr0 + sum0;                            // partial sums (this thread's keys); added up at the end
         l[1] = l[1] * corr1 + sum1;
         // ---- o = o * corr + p v over this warp's half of the latent columns ------------------------------------------
         {
@@ -197,6 +210,11 @@ latent_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_r
     l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
     l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1);
     l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+    __syncthreads();                                           // (the exchange buffers of the last tile are free)
+    if (cq == 0) xm[half * 16 + g] = l[0], xm[half * 16 + g + 8] = l[1];
+    pair_sync(rg);
+    l[0] += xm[(half ^ 1) * 16 + g];                           // both warps form the same sum: a + b = b + a
+    l[1] += xm[(half ^ 1) * 16 + g + 8];
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
         const int r = x ? row_b : row_a;
@@ -269,7 +287,7 @@ int launch_one(const float* q_lat, const float* q_rot, long long head_rows, bf16
                int page_size, float scale, int chunk, int splits, cudaStream_t stream) {
     auto kern = latent_mma_kernel<C, ROWG, STAGES>;
     const int LD = C + R + 8;
-    const size_t sh = (size_t)(ROWG * 16 + STAGES * KT) * LD * sizeof(bf16);
+    const size_t sh = (size_t)(ROWG * 16 + STAGES * KT) * LD * sizeof(bf16) + (size_t)ROWG * (64 * 16 + 32 * 4);
     if (sh > 48 * 1024) {
         cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sh);
         if (err != cudaSuccess) {

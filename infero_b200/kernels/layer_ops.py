@@ -299,23 +299,31 @@ def add_layernorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.
                                       _stream()))
 
 
-def hyper_step(xs: torch.Tensor, y: Optional[torch.Tensor], mix: Optional[torch.Tensor], w_out: Optional[torch.Tensor],
+def hyper_step(xs: torch.Tensor, y, mix: Optional[torch.Tensor], w_out: Optional[torch.Tensor],
                w_in: Optional[torch.Tensor], norm_w: Optional[torch.Tensor], eps: float, h_out: Optional[torch.Tensor],
                u_out: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> None:
-    """One pass over the streams xs (float32 [T, S, d]) of every token: with ``y`` (float32 [T, d]) the update
-    xs[r] <- sum_s mix[s, r] xs[s] + w_out[r] y; with ``w_in`` and ``norm_w`` the next sublayer's input
-    h_out = layer norm(sum_s w_in[s] xs[s]); with ``u_out`` (float32) and no norm the weighted sum itself (w_in None:
-    the plain sum).  ``rows``: work on these tokens only."""
+    """One pass over the streams xs (float32 [T, S, d]) of every token: with ``y`` (float32 [T, d], or a product left as
+    ``Partials``) the update xs[r] <- sum_s mix[s, r] xs[s] + w_out[r] y; with ``w_in`` and ``norm_w`` the next
+    sublayer's input h_out = layer norm(sum_s w_in[s] xs[s]); with ``u_out`` (float32) and no norm the weighted sum itself
+    (w_in None: the plain sum).  ``rows``: work on these tokens only."""
+    from . import Partials
     T, S, d = xs.shape
     assert xs.dtype == torch.float32 and xs.is_contiguous()
-    assert y is None or (y.dtype == torch.float32 and y.shape == (T, d) and y.stride(1) == 1)
+    splits, split_stride, y_stride = 1, 0, 0
+    if isinstance(y, Partials):
+        assert y.bias is None and tuple(y.shape) == (T, d)
+        y, splits, split_stride, y_stride = y.data, y.splits, y.split_stride, d
+    elif y is not None:
+        assert y.dtype == torch.float32 and y.shape == (T, d) and y.stride(1) == 1
+        y_stride = y.stride(0)
     n = T if rows is None else rows.numel()
     for o in (h_out, u_out):
         assert o is None or (o.is_contiguous() and tuple(o.shape) == (n, d))
     assert u_out is None or u_out.dtype == torch.float32
-    _check(lib().infero_hyper_step(_ptr(xs), _ptr(y), c_int(y.stride(0) if y is not None else 0), _ptr(_f32(mix, "mix")),
-                                   _ptr(_f32(w_out, "w_out")), _ptr(_f32(w_in, "w_in")), _ptr(_f32(norm_w, "norm_w")),
-                                   c_float(eps), _ptr(h_out), c_int(_dt(h_out) if h_out is not None else 0), _ptr(u_out),
+    _check(lib().infero_hyper_step(_ptr(xs), _ptr(y), c_int(y_stride), c_int(splits), c_longlong(split_stride),
+                                   _ptr(_f32(mix, "mix")), _ptr(_f32(w_out, "w_out")), _ptr(_f32(w_in, "w_in")),
+                                   _ptr(_f32(norm_w, "norm_w")), c_float(eps), _ptr(h_out),
+                                   c_int(_dt(h_out) if h_out is not None else 0), _ptr(u_out),
                                    _ptr(None if rows is None else _i32(rows, "rows")), c_int(n), c_int(S), c_int(d), _stream()))
 
 

@@ -122,12 +122,15 @@ class DecoderModel:
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         R = logit_rows.numel()
-        total = torch.empty((R, s.hidden), dtype=torch.float32, device=x0.device)
-        if pending is not None:
-            L.hyper_step(x, pending[0], pending[1], pending[2], None, None, 0.0, None, u_out=total, rows=logit_rows)
+        y, mix, w_out = pending if pending is not None else (None, None, None)
+        if getattr(self.final_norm.spec, "kind", "") == "layernorm":
+            # the last update, the sum of the streams and the final norm of the wanted rows in one pass
+            h = torch.empty((R, s.hidden), dtype=ctx.act_dtype, device=x0.device)
+            L.hyper_step(x, y, mix, w_out, None, self.final_norm.weight, self.final_norm.spec.eps, h, rows=logit_rows)
         else:
-            L.hyper_step(x, None, None, None, None, None, 0.0, None, u_out=total, rows=logit_rows)
-        h = self.final_norm.forward(ctx, total, None)
+            total = torch.empty((R, s.hidden), dtype=torch.float32, device=x0.device)
+            L.hyper_step(x, y, mix, w_out, None, None, 0.0, None, u_out=total, rows=logit_rows)
+            h = self.final_norm.forward(ctx, total, None)
         logits = self.head.forward(h, out_dtype=torch.float32)
         if s.logit_scale != 1.0:
             logits.mul_(s.logit_scale)

@@ -223,11 +223,13 @@ class HyperPreNormBlock(Part):
 
     @staticmethod
     def _as_f32(y):
+        """A sublayer's result as the stream kernel takes it: float32, or a product left as partial sums without a bias
+        (the kernel adds them up in its own pass)."""
         from .. import kernels as K
         if hasattr(y, "as_partials"):
             y = y.as_partials()
         if isinstance(y, K.Partials):
-            return y.materialize(torch.float32)
+            return y if y.bias is None else y.materialize(torch.float32)
         return y if y.dtype == torch.float32 else y.float()
 
     def forward(self, ctx, x, delta, slot):

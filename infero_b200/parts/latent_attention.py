@@ -103,4 +103,4 @@ class LatentAttention(Mixer):
         attn = torch.empty((T, H * V), dtype=h.dtype, device=dev)
         gate = proj[:, self.gate_off:self.gate_off + H] if self.spec.out_gate else None
         A.finish(val, gate, attn, T, H, V)
-        return self.out.forward(attn, residual=True, out_dtype=torch.float32)
+        return self.out.forward(attn, defer=True, residual=True)

@@ -261,7 +261,10 @@ class _Latent:
             h_q_len=np.array(q_len, dtype=np.int32), h_pos0=np.array(pos0, dtype=np.int32), kv_bound=None,
             max_kv_len=max(p + n for p, n in zip(pos0, q_len)), kv_cache=lambda slot: kv, block_table=lambda group: table)
         h = torch.cat([rows for _, rows in entries]).to(self.td).to(DEV)
-        out = self.part.forward(ctx, h, types.SimpleNamespace(cache=0, write_cache=True)).float().cpu()
+        out = self.part.forward(ctx, h, types.SimpleNamespace(cache=0, write_cache=True))
+        if hasattr(out, "materialize"):                                   # a product of few rows left as partial sums
+            out = out.materialize(torch.float32)
+        out = out.float().cpu()
         return {rid: out[q_start[e]:q_start[e] + q_len[e]] for e, (rid, _) in enumerate(entries)}
 
 
