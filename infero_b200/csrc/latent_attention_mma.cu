@@ -46,7 +46,10 @@ latent_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_r
 
     // ---- which request, which of its tokens ---------------------------------------------------------------
     int e = entry_first, t0 = 0;
-    {
+    if (TQ == 1 && ROWG < 4) {
+        e = entry_first + blockIdx.x;                          // single tokens: a tile is a request
+        if (e >= n_entries) return;
+    } else {
         int tile = blockIdx.x;
         for (; e < n_entries; ++e) {
             const int n = (entry_q_len[e] + TQ - 1) / TQ;
@@ -64,44 +67,53 @@ latent_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_r
     const int k_hi = min(pos_first + n_tq, splits > 1 ? k_lo + chunk : 0x7fffffff);     // one past the last key
     const int* table = block_table + (size_t)e * max_blocks;
 
-    // a tile row is fetched by NT / KT threads: one look-up of its page, then its 16-byte chunks back to back
-    auto load_tile = [&](int stage, int key0) {
-        constexpr int PER_ROW = NT / KT;
-        const int r = tid / PER_ROW, c0 = tid % PER_ROW;
-        const int j = key0 + r;
-        bf16* d = k_s + ((size_t)stage * KT + r) * LD;
+    // a tile row is fetched by NT / KT threads: its page was looked up while the tile before was being worked on
+    // (`page_of` for the tile after is issued right behind the copies), then its 16-byte chunks go back to back
+    constexpr int PER_ROW = NT / KT;
+    const int lr = tid / PER_ROW, lc0 = tid % PER_ROW;
+    auto page_of = [&](int key0) {
+        const int j = key0 + lr;
+        return (j >= k_lo && j < k_hi) ? table[j / page_size] : -1;
+    };
+    auto load_tile = [&](int stage, int key0, int page) {
+        const int j = key0 + lr;
+        bf16* d = k_s + ((size_t)stage * KT + lr) * LD;
         const int CH = W / 8;
-        int page = -1;
-        if (j >= k_lo && j < k_hi) page = table[j / page_size];
         if (page >= 0) {
             const bf16* src = cache + ((size_t)page * page_size + (j % page_size)) * W;
-            for (int c = c0; c < CH; c += PER_ROW) cp_async16(smem_addr(d + c * 8), src + c * 8);
+            for (int c = lc0; c < CH; c += PER_ROW) cp_async16(smem_addr(d + c * 8), src + c * 8);
         } else {
-            for (int c = c0; c < CH; c += PER_ROW) *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0, 0, 0, 0);
+            for (int c = lc0; c < CH; c += PER_ROW) *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0, 0, 0, 0);
         }
     };
     const int key_begin = (k_lo / KT) * KT;
     const int n_tiles = k_hi > key_begin ? (k_hi - key_begin + KT - 1) / KT : 0;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < n_tiles) load_tile(s, key_begin + s * KT);
+        if (s < n_tiles) load_tile(s, key_begin + s * KT, page_of(key_begin + s * KT));
         cp_async_commit();
     }
+    int page_next = STAGES - 1 < n_tiles ? page_of(key_begin + (STAGES - 1) * KT) : -1;
     // ---- queries: float32 -> bf16 rows [latent part | rotated part]; rows without a token or head are zero -------
-    // (four values per load, several loads in flight: a row's parts are multiples of 16 wide)
+    // (64 threads a row, four values per load, the loads of four rows in flight together; no division in the loop: with
+    // two warps a CTA every instruction counts)
     {
         const int W4 = W / 4, C4 = C / 4;
-#pragma unroll 8
-        for (int i = tid; i < ROWS * W4; i += NT) {
-            const int r = i / W4, c = i - r * W4;
-            const int tq = r / HC, n = head0 + r % HC;
+        constexpr int RPI = NT / 64;                           // rows per pass
+        const int sub = tid >> 6, c_first = tid & 63;
+#pragma unroll 4
+        for (int r = sub; r < ROWS; r += RPI) {
+            const int tq = r / HC, n = head0 + r - tq * HC;
             const bool live = tq < n_tq && n < H;
             const size_t row = live ? (size_t)n * head_rows + tok0 + tq : 0;
-            const float4* src = c < C4 ? reinterpret_cast<const float4*>(q_lat + row * C) + c
-                                       : reinterpret_cast<const float4*>(q_rot + row * R) + (c - C4);
-            float4 v = __ldg(src);
-            if (!live) v = make_float4(0.f, 0.f, 0.f, 0.f);
-            *reinterpret_cast<uint2*>(q_s + (size_t)r * LD + c * 4) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+            const float4* lat = reinterpret_cast<const float4*>(q_lat + row * C);
+            const float4* rot = reinterpret_cast<const float4*>(q_rot + row * R) - C4;
+            bf16* dst = q_s + (size_t)r * LD;
+            for (int c = c_first; c < W4; c += 64) {
+                float4 v = __ldg(c < C4 ? lat + c : rot + c);
+                if (!live) v = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<uint2*>(dst + c * 4) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+            }
         }
     }
 
@@ -116,25 +128,43 @@ latent_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_r
     for (int kt = 0; kt < n_tiles; ++kt) {
         cp_async_wait<STAGES - 2>();
         __syncthreads();                                       // tile kt has landed (and the queries); tile kt - 1 is free
-        if (kt + STAGES - 1 < n_tiles) load_tile((kt + STAGES - 1) % STAGES, key_begin + (kt + STAGES - 1) * KT);
+        if (kt + STAGES - 1 < n_tiles) load_tile((kt + STAGES - 1) % STAGES, key_begin + (kt + STAGES - 1) * KT, page_next);
         cp_async_commit();
+        page_next = kt + STAGES < n_tiles ? page_of(key_begin + (kt + STAGES) * KT) : -1;
         const bf16* kt_s = k_s + (size_t)(kt % STAGES) * KT * LD;
         const int key0 = key_begin + kt * KT;
         // ---- s = q k^T for this warp's 16 of the tile's 32 keys: two n-tiles of 8 keys, W / 16 k-steps -------------------
-        float s[2][4];
+        float s[2][4], s2[2][4];                               // (two sets, even and odd k-steps: shorter chains of dependent products)
 #pragma unroll
-        for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+        for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = s2[i][0] = s2[i][1] = s2[i][2] = s2[i][3] = 0.f;
         {
             const bf16* qa = q_s + (size_t)(rg * 16 + (lane & 7) + (mi & 1) * 8) * LD + (mi >> 1) * 8;
             const bf16* kb = kt_s + (size_t)(half * 16 + (mi >> 1) * 8 + (lane & 7)) * LD + (mi & 1) * 8;
-#pragma unroll 4
-            for (int ks = 0; ks < W / 16; ++ks) {
+            const int n_ks = W / 16;
+            int ks = 0;
+#pragma unroll 2
+            for (; ks + 2 <= n_ks; ks += 2) {
+                uint32_t a[4], b[4], a2[4], b2[4];
+                ldmatrix_x4(a, smem_addr(qa + ks * 16));
+                ldmatrix_x4(b, smem_addr(kb + ks * 16));
+                ldmatrix_x4(a2, smem_addr(qa + ks * 16 + 16));
+                ldmatrix_x4(b2, smem_addr(kb + ks * 16 + 16));
+                mma16816(s[0], a, b[0], b[1]);
+                mma16816(s[1], a, b[2], b[3]);
+                mma16816(s2[0], a2, b2[0], b2[1]);
+                mma16816(s2[1], a2, b2[2], b2[3]);
+            }
+            if (ks < n_ks) {
                 uint32_t a[4], b[4];
                 ldmatrix_x4(a, smem_addr(qa + ks * 16));
                 ldmatrix_x4(b, smem_addr(kb + ks * 16));
                 mma16816(s[0], a, b[0], b[1]);
                 mma16816(s[1], a, b[2], b[3]);
             }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int x = 0; x < 4; ++x) s[i][x] += s2[i][x];
         }
         // ---- mask; the rows' maxima over all 32 keys, through the pair's exchange -------------------------------------
         float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
