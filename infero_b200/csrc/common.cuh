@@ -25,7 +25,8 @@ __device__ __forceinline__ float load_any(const void* p, int dtype, size_t i) {
 // Gated activations of a feed-forward layer, from a gate g and an up value u:
 //   GLU_SILU:    silu(g) * u
 //   GLU_CLAMPED: g' = min(g, limit), u' = clamp(u, -limit, limit);  g' * sigmoid(alpha * g') * (u' + 1)
-enum : int { GLU_SILU = 0, GLU_CLAMPED = 1 };
+//   ACT_RELU2 (not gated, one value): max(v, 0)^2
+enum : int { GLU_SILU = 0, GLU_CLAMPED = 1, ACT_RELU2 = 2 };
 __device__ __forceinline__ float glu_act(float g, float u, int kind, float limit, float alpha) {
     if (kind == GLU_CLAMPED) {
         g = fminf(g, limit);

@@ -473,6 +473,13 @@ __device__ __forceinline__ void drain_accumulator(uint32_t lane_addr, int ra, in
                         for (int e = 0; e < 16; ++e)
                             if (rb + e < RB) v[e] += load_any(bias, bias_dtype, rb + e);
                     }
+                    if (act_kind == ACT_RELU2) {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) {
+                            const float r = fmaxf(v[e], 0.f);
+                            v[e] = r * r;
+                        }
+                    }
                     if (rb + 16 <= RB) {
                         store16<OutT>(dst, v, (reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
                     } else {
@@ -1375,6 +1382,27 @@ int infero_gemm_tc_swiglu(const void* x, const void* w, void* out, int M, int N,
         if (r >= 0) return r;
     }
     return launch_persistent<EPI_ROW_SWIGLU, bf16>(x, w, out, nullptr, 0, M, N, K, ldx, ldc, sm_count, err, stream);
+}
+
+// A product of many rows with an activation in the epilogue of the persistent kernel (bf16 out):
+//   ACT_RELU2:               out[M, N]     = max(x w^T, 0)^2
+//   GLU_SILU / GLU_CLAMPED:  out[M, N / 2] = glu_act(g, u) with w's rows alternating gate and up
+// Returns 2, with nothing launched, for M <= 256 (few rows take the split-K path and an activation kernel behind it).
+int infero_gemm_tc_act(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldc, int act_kind,
+                       float act_limit, float act_alpha, int sm_count, cudaStream_t stream) {
+    if (M == 0 || N == 0) return 0;
+    if (M <= 256) return 2;
+    INFERO_REQUIRE(infero_gemm_tc_supported(x, w, M, N, K, ldx), "gemm_tc_act: shape M=%d N=%d K=%d ldx=%d not supported", M, N, K, ldx);
+    int* err;
+    if (err_flag_ptr(&err)) return 1;
+    if (act_kind == ACT_RELU2) {
+        INFERO_REQUIRE(ldc >= N, "gemm_tc_act: ldc=%d below N=%d", ldc, N);
+        return launch_persistent<EPI_ROW, bf16>(x, w, out, nullptr, 0, M, N, K, ldx, ldc, sm_count, err, stream, nullptr, 1,
+                                                act_kind, act_limit, act_alpha);
+    }
+    INFERO_REQUIRE(N % 2 == 0 && ldc >= N / 2, "gemm_tc_act: N=%d must be even and ldc=%d at least N/2", N, ldc);
+    return launch_persistent<EPI_ROW_SWIGLU, bf16>(x, w, out, nullptr, 0, M, N, K, ldx, ldc, sm_count, err, stream, nullptr, 1,
+                                                   act_kind, act_limit, act_alpha);
 }
 
 // A grouped product on the persistent kernel: x [M, K] in tiles of 128 rows, w n_groups stacked [N, K] matrices,

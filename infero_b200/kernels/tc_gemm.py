@@ -95,6 +95,28 @@ def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     return True
 
 
+ACT_KINDS = {"swiglu": 0, "glu_clamped": 1, "relu2": 2}
+
+
+def gemm_act(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str, limit: float = 0.0, alpha: float = 1.0) -> bool:
+    """A product of many rows with its activation in the epilogue (bf16): "relu2": out[M, N] = max(a @ w^T, 0)^2; "swiglu" /
+    "glu_clamped": out[M, N / 2] from columns (2j, 2j + 1) as gate and up.  Returns False (nothing launched) for 256 rows
+    and fewer or shapes the tensor-core product does not take."""
+    from ctypes import c_float
+    M, K = a.shape
+    N = w.shape[0]
+    if M <= 256 or out.dtype != torch.bfloat16 or not supported(a, w):
+        return False
+    assert w.shape[1] == K and out.stride(1) == 1 and out.shape == (M, N if kind == "relu2" else N // 2)
+    rc = lib().infero_gemm_tc_act(_ptr(a), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
+                                  c_int(out.stride(0)), c_int(ACT_KINDS[kind]), c_float(limit), c_float(alpha),
+                                  c_int(sm_count(a.device)), _stream())
+    if rc == 2:
+        return False
+    _check(rc)
+    return True
+
+
 def partials(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """float32 [splits, M, N] whose sum over the first axis is a @ w^T (M <= 256)."""
     M, K = a.shape

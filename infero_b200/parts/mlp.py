@@ -66,9 +66,13 @@ class GluMlp(SwiGluMlp):
         s = self.spec
         if s.activation == "swiglu":
             return super().forward(ctx, h)
-        from ..kernels import layer_ops as L
+        from ..kernels import layer_ops as L, tc_gemm
         act = torch.empty((h.shape[0], s.intermediate), dtype=h.dtype, device=h.device)
-        L.glu_act(self.gate_up.forward(h, defer=True), act, (s.activation, s.limit, s.act_alpha))
+        # many rows in bf16: the activation in the product's epilogue; else the product (as partial sums where it is cut)
+        # and the activation kernel
+        if not (h.dtype == torch.bfloat16 and self.gate_up.weight.dtype == torch.bfloat16
+                and tc_gemm.gemm_act(h, self.gate_up.weight, act, s.activation, s.limit, s.act_alpha)):
+            L.glu_act(self.gate_up.forward(h, defer=True), act, (s.activation, s.limit, s.act_alpha))
         return self.down.forward(act, defer=True, residual=True)
 
 
@@ -93,7 +97,9 @@ class Relu2Mlp(FeedForward):
         self.down = Linear(tensors[self._n("down")], None, self._n("down"))
 
     def forward(self, ctx, h):
-        from ..kernels import layer_ops as L
+        from ..kernels import layer_ops as L, tc_gemm
         act = torch.empty((h.shape[0], self.spec.intermediate), dtype=h.dtype, device=h.device)
-        L.relu2(self.up.forward(h, defer=True), act)
+        if not (h.dtype == torch.bfloat16 and self.up.weight.dtype == torch.bfloat16
+                and tc_gemm.gemm_act(h, self.up.weight, act, "relu2")):
+            L.relu2(self.up.forward(h, defer=True), act)
         return self.down.forward(act, defer=True, residual=True)

@@ -100,6 +100,26 @@ def test_relu2_and_the_clamped_gated_activation():
     assert _rel(act, gate * torch.sigmoid(gate) * up) < 1e-6
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 96, 64), (700, 256, 128), (1030, 520, 72)])
+def test_activations_in_the_epilogue_of_the_many_row_product(M, N, K):
+    """Squared relu and the clamped gated activation inside the tcgen05 product's epilogue against product-then-activation
+    in 64-bit; 256 rows and fewer are refused (they take the split-K path and the activation kernel)."""
+    from infero_b200.kernels import tc_gemm
+    g = torch.Generator().manual_seed(M)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.3).to(torch.bfloat16)
+    ref = a.double() @ w.double().T
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    assert tc_gemm.gemm_act(a.to(DEV), w.to(DEV), out, "relu2")
+    assert _rel(out, torch.relu(ref).pow(2)) < 1e-2
+    out = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
+    assert tc_gemm.gemm_act(a.to(DEV), w.to(DEV), out, "glu_clamped", 1.5, 1.702)
+    gate, up = ref[:, 0::2].clamp(max=1.5), ref[:, 1::2].clamp(-1.5, 1.5)
+    assert _rel(out, gate * torch.sigmoid(1.702 * gate) * (up + 1)) < 1e-2
+    assert float((ref[:, 0::2] > 1.5).float().mean()) > 0.05
+    assert not tc_gemm.gemm_act(a[:200].to(DEV), w.to(DEV), out[:200], "glu_clamped", 1.5, 1.702)
+
+
 def test_rotary_tables_on_the_device_and_both_pairings():
     """The prepare kernel's rotation against the plain one: stretched frequencies with their amplitude, both pairings,
     fewer rotated coordinates than the part is wide, positions far out."""
