@@ -5,10 +5,11 @@
 // heads of one request (HC = 16, 32 or 64 heads; TQ = 1 for single tokens, 64 / HC in a prompt portion) and walks
 // the request's keys in tiles of 32, fetched once for all its rows by cp.async into a ring in shared memory.
 // Queries arrive as float32 (the plain parts already carried through Wuk^T) and are rounded to bf16 into shared
-// memory once; scores, running maximum and sum are 32-bit.  Two warps share 16 rows: each forms the rows' scores
-// with 16 of a tile's 32 keys, they exchange the rows' maxima and their softmax weights (as tensor-core fragments,
-// whose layout is the same lane by lane) through shared memory, and each owns one half of the C result columns, so
-// the result tile of 16 x C/2 stays in registers.  Key tiles start at multiples of 32 of the absolute position, so what is
+// memory once; scores, running maximum and sum are 32-bit.  Two warps share 16 rows (four for single tokens with a
+// latent of 256 and more, where a CTA has few rows and the length of a warp's instruction chain is what counts): each
+// forms the rows' scores with its share of a tile's 32 keys, they exchange the rows' maxima and their softmax weights
+// (as tensor-core fragments, whose layout is the same lane by lane) through shared memory, and each owns its share of the
+// C result columns, so the result tile of 16 x C/2 (or C/4) stays in registers.  Key tiles start at multiples of 32 of the absolute position, so what is
 // computed for a token does not depend on how its prompt was cut.
 //
 // Single tokens with long contexts are cut into `splits` ranges of keys, one CTA each; every CTA leaves its
@@ -21,28 +22,31 @@ using namespace attn;
 
 constexpr int KT = 32;                        // keys per tile
 
-// a barrier of the two warps that share 16 rows (barrier 0 is the block's)
-__device__ __forceinline__ void pair_sync(int rg) { asm volatile("bar.sync %0, 64;" ::"r"(rg + 1) : "memory"); }
+// a barrier of the NW warps that share 16 rows (barrier 0 is the block's)
+template <int NW>
+__device__ __forceinline__ void group_sync(int rg) { asm volatile("bar.sync %0, %1;" ::"r"(rg + 1), "n"(NW * 32) : "memory"); }
 
-template <int C, int ROWG, int STAGES>
-__global__ void __launch_bounds__(ROWG * 64, 1)
+// NW = 2 or 4 warps share 16 rows: each forms the scores of 32 / NW of a tile's keys and owns C / NW result columns.
+template <int C, int ROWG, int STAGES, int NW>
+__global__ void __launch_bounds__(ROWG * NW * 32, 1)
 latent_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_rot, long long head_rows,
                   bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                   const bf16* __restrict__ cache, const int* __restrict__ block_table, int max_blocks,
                   const int* __restrict__ entry_q_start, const int* __restrict__ entry_q_len,
                   const int* __restrict__ entry_pos0, int entry_first, int n_entries, int TQ, int HC, int H, int R,
                   int page_size, float scale_log2, int chunk, int splits) {
-    constexpr int ROWS = ROWG * 16, NT = ROWG * 64, CW = C / 2, NO = CW / 8;
+    constexpr int ROWS = ROWG * 16, NT = ROWG * NW * 32, CW = C / NW, NO = CW / 8;
+    constexpr int KW = KT / NW, NTW = KW / 8;              // keys, and n-tiles of 8 keys, whose scores a warp forms
     const int W = C + R, LD = W + 8;                       // padded row of a tile, in elements
     extern __shared__ __align__(16) uint8_t smem[];
     bf16* q_s = reinterpret_cast<bf16*>(smem);             // [ROWS][LD]
     bf16* k_s = q_s + ROWS * LD;                           // [STAGES][KT][LD]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int rg = warp >> 1, half = warp & 1;
-    // what the two warps of 16 rows hand each other: row maxima (and, at the end, sums), and their softmax weights as
-    // tensor-core fragments
-    uint4* xp = reinterpret_cast<uint4*>(k_s + (size_t)STAGES * KT * LD) + rg * 64;          // [2][32]
-    float* xm = reinterpret_cast<float*>(reinterpret_cast<uint4*>(k_s + (size_t)STAGES * KT * LD) + ROWG * 64) + rg * 32;   // [2][16]
+    const int rg = warp / NW, part = warp % NW;
+    // what the warps of 16 rows hand one another: their softmax weights as tensor-core fragments ([k-step of 16 keys][register]
+    // [lane]: the fragment layout is the same in every warp, lane by lane), row maxima and, at the end, sums
+    uint32_t* xp = reinterpret_cast<uint32_t*>(k_s + (size_t)STAGES * KT * LD) + rg * 256;    // [2][4][32]
+    float* xm = reinterpret_cast<float*>(reinterpret_cast<uint32_t*>(k_s + (size_t)STAGES * KT * LD) + ROWG * 256) + rg * 64;   // [NW][16]
 
     // ---- which request, which of its tokens ---------------------------------------------------------------
     int e = entry_first, t0 = 0;
@@ -133,46 +137,69 @@ latent_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_r
         page_next = kt + STAGES < n_tiles ? page_of(key_begin + (kt + STAGES) * KT) : -1;
         const bf16* kt_s = k_s + (size_t)(kt % STAGES) * KT * LD;
         const int key0 = key_begin + kt * KT;
-        // ---- s = q k^T for this warp's 16 of the tile's 32 keys: two n-tiles of 8 keys, W / 16 k-steps -------------------
-        float s[2][4], s2[2][4];                               // (two sets, even and odd k-steps: shorter chains of dependent products)
+        // ---- s = q k^T for this warp's KW of the tile's 32 keys: NTW n-tiles of 8 keys, W / 16 k-steps; two sets of sums
+        // (even and odd k-steps) keep the chains of dependent products short ----------------------------------------------------
+        float s[NTW][4], s2[NTW][4];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = s2[i][0] = s2[i][1] = s2[i][2] = s2[i][3] = 0.f;
+        for (int i = 0; i < NTW; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = s2[i][0] = s2[i][1] = s2[i][2] = s2[i][3] = 0.f;
         {
             const bf16* qa = q_s + (size_t)(rg * 16 + (lane & 7) + (mi & 1) * 8) * LD + (mi >> 1) * 8;
-            const bf16* kb = kt_s + (size_t)(half * 16 + (mi >> 1) * 8 + (lane & 7)) * LD + (mi & 1) * 8;
             const int n_ks = W / 16;
             int ks = 0;
+            if (NW == 2) {
+                // one load brings 16 keys x 16 of the contraction
+                const bf16* kb = kt_s + (size_t)(part * 16 + (mi >> 1) * 8 + (lane & 7)) * LD + (mi & 1) * 8;
 #pragma unroll 2
-            for (; ks + 2 <= n_ks; ks += 2) {
-                uint32_t a[4], b[4], a2[4], b2[4];
-                ldmatrix_x4(a, smem_addr(qa + ks * 16));
-                ldmatrix_x4(b, smem_addr(kb + ks * 16));
-                ldmatrix_x4(a2, smem_addr(qa + ks * 16 + 16));
-                ldmatrix_x4(b2, smem_addr(kb + ks * 16 + 16));
-                mma16816(s[0], a, b[0], b[1]);
-                mma16816(s[1], a, b[2], b[3]);
-                mma16816(s2[0], a2, b2[0], b2[1]);
-                mma16816(s2[1], a2, b2[2], b2[3]);
-            }
-            if (ks < n_ks) {
-                uint32_t a[4], b[4];
-                ldmatrix_x4(a, smem_addr(qa + ks * 16));
-                ldmatrix_x4(b, smem_addr(kb + ks * 16));
-                mma16816(s[0], a, b[0], b[1]);
-                mma16816(s[1], a, b[2], b[3]);
+                for (; ks + 2 <= n_ks; ks += 2) {
+                    uint32_t a[4], b[4], a2[4], b2[4];
+                    ldmatrix_x4(a, smem_addr(qa + ks * 16));
+                    ldmatrix_x4(b, smem_addr(kb + ks * 16));
+                    ldmatrix_x4(a2, smem_addr(qa + ks * 16 + 16));
+                    ldmatrix_x4(b2, smem_addr(kb + ks * 16 + 16));
+                    mma16816(s[0], a, b[0], b[1]);
+                    mma16816(s[NTW - 1], a, b[2], b[3]);
+                    mma16816(s2[0], a2, b2[0], b2[1]);
+                    mma16816(s2[NTW - 1], a2, b2[2], b2[3]);
+                }
+                if (ks < n_ks) {
+                    uint32_t a[4], b[4];
+                    ldmatrix_x4(a, smem_addr(qa + ks * 16));
+                    ldmatrix_x4(b, smem_addr(kb + ks * 16));
+                    mma16816(s[0], a, b[0], b[1]);
+                    mma16816(s[NTW - 1], a, b[2], b[3]);
+                }
+            } else {
+                // one load brings 8 keys x 32 of the contraction: two k-steps
+                const bf16* kb = kt_s + (size_t)(part * 8 + (lane & 7)) * LD + mi * 8;
+#pragma unroll 2
+                for (; ks + 2 <= n_ks; ks += 2) {
+                    uint32_t a[4], a2[4], b[4];
+                    ldmatrix_x4(a, smem_addr(qa + ks * 16));
+                    ldmatrix_x4(a2, smem_addr(qa + ks * 16 + 16));
+                    ldmatrix_x4(b, smem_addr(kb + ks * 16));
+                    mma16816(s[0], a, b[0], b[1]);
+                    mma16816(s2[0], a2, b[2], b[3]);
+                }
+                if (ks < n_ks) {
+                    // the last, single k-step: the load's second half stays inside the row's padding and is not used
+                    uint32_t a[4], b[4];
+                    ldmatrix_x4(a, smem_addr(qa + ks * 16));
+                    ldmatrix_x4(b, smem_addr(kt_s + (size_t)(part * 8 + (lane & 7)) * LD + (mi & 1) * 8 + ks * 16));
+                    mma16816(s[0], a, b[0], b[1]);
+                }
             }
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
+            for (int i = 0; i < NTW; ++i)
 #pragma unroll
                 for (int x = 0; x < 4; ++x) s[i][x] += s2[i][x];
         }
-        // ---- mask; the rows' maxima over all 32 keys, through the pair's exchange -------------------------------------
+        // ---- mask; the rows' maxima over all 32 keys, through the group's exchange -------------------------------------
         float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+        for (int nt = 0; nt < NTW; ++nt)
 #pragma unroll
             for (int x = 0; x < 2; ++x) {
-                const int j = key0 + half * 16 + nt * 8 + cq * 2 + x;
+                const int j = key0 + part * KW + nt * 8 + cq * 2 + x;
                 const bool in = j >= k_lo && j < k_hi;
                 const float a = (in && j <= hi0) ? s[nt][x] * scale_log2 : -CUDART_INF_F;
                 const float b = (in && j <= hi1) ? s[nt][2 + x] * scale_log2 : -CUDART_INF_F;
@@ -183,41 +210,43 @@ latent_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_r
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        if (cq == 0) xm[half * 16 + g] = mx0, xm[half * 16 + g + 8] = mx1;
-        pair_sync(rg);
-        mx0 = fmaxf(mx0, xm[(half ^ 1) * 16 + g]);
-        mx1 = fmaxf(mx1, xm[(half ^ 1) * 16 + g + 8]);
+        if (cq == 0) xm[part * 16 + g] = mx0, xm[part * 16 + g + 8] = mx1;
+        group_sync<NW>(rg);
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            mx0 = fmaxf(mx0, xm[w * 16 + g]);
+            mx1 = fmaxf(mx1, xm[w * 16 + g + 8]);
+        }
         const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
         const float sub0 = mn0 == -CUDART_INF_F ? 0.f : mn0, sub1 = mn1 == -CUDART_INF_F ? 0.f : mn1;
         const float corr0 = exp2f(m[0] - sub0), corr1 = exp2f(m[1] - sub1);
         m[0] = mn0, m[1] = mn1;
         float sum0 = 0.f, sum1 = 0.f;
-        uint32_t pf[2][4];                                     // two k-steps of 16 keys: this warp's and its partner's
+        uint32_t pf[2][4];                                     // the tile's two k-steps of 16 keys
         {
-            float p[2][4];
+            // this warp's weights go to their place among the fragments: n-tile t of the tile's four is registers
+            // (t & 1) * 2, + 1 of k-step t >> 1
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                p[nt][0] = exp2f(s[nt][0] - sub0);
-                p[nt][1] = exp2f(s[nt][1] - sub0);
-                p[nt][2] = exp2f(s[nt][2] - sub1);
-                p[nt][3] = exp2f(s[nt][3] - sub1);
-                sum0 += p[nt][0] + p[nt][1];
-                sum1 += p[nt][2] + p[nt][3];
+            for (int nt = 0; nt < NTW; ++nt) {
+                const float p0 = exp2f(s[nt][0] - sub0), p1 = exp2f(s[nt][1] - sub0);
+                const float p2 = exp2f(s[nt][2] - sub1), p3 = exp2f(s[nt][3] - sub1);
+                sum0 += p0 + p1;
+                sum1 += p2 + p3;
+                const int t = part * NTW + nt;
+                xp[((t >> 1) * 4 + (t & 1) * 2) * 32 + lane] = pack_bf16(p0, p1);
+                xp[((t >> 1) * 4 + (t & 1) * 2 + 1) * 32 + lane] = pack_bf16(p2, p3);
             }
-            const uint4 own = make_uint4(pack_bf16(p[0][0], p[0][1]), pack_bf16(p[0][2], p[0][3]), pack_bf16(p[1][0], p[1][1]),
-                                         pack_bf16(p[1][2], p[1][3]));
-            xp[half * 32 + lane] = own;                        // the fragment layout is the same in both warps, lane by lane
-            pair_sync(rg);
-            const uint4 other = xp[(half ^ 1) * 32 + lane];
-            const uint4 lo = half ? other : own, hi = half ? own : other;       // keys 0..15 and 16..31 of the tile
-            pf[0][0] = lo.x, pf[0][1] = lo.y, pf[0][2] = lo.z, pf[0][3] = lo.w;
-            pf[1][0] = hi.x, pf[1][1] = hi.y, pf[1][2] = hi.z, pf[1][3] = hi.w;
+            group_sync<NW>(rg);
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) pf[kk][r] = xp[(kk * 4 + r) * 32 + lane];
         }
         l[0] = l[0] * corr0 + sum0;                            // partial sums (this thread's keys); added up at the end
         l[1] = l[1] * corr1 + sum1;
         // ---- o = o * corr + p v over this warp's half of the latent columns ------------------------------------------
         {
-            const bf16* vb = kt_s + (size_t)((mi & 1) * 8 + (lane & 7)) * LD + half * CW + (mi >> 1) * 8;
+            const bf16* vb = kt_s + (size_t)((mi & 1) * 8 + (lane & 7)) * LD + part * CW + (mi >> 1) * 8;
 #pragma unroll
             for (int np = 0; np < NO / 2; ++np) {
                 float* o0 = o[np * 2];
@@ -241,10 +270,14 @@ latent_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_r
     l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1);
     l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
     __syncthreads();                                           // (the exchange buffers of the last tile are free)
-    if (cq == 0) xm[half * 16 + g] = l[0], xm[half * 16 + g + 8] = l[1];
-    pair_sync(rg);
-    l[0] += xm[(half ^ 1) * 16 + g];                           // both warps form the same sum: a + b = b + a
-    l[1] += xm[(half ^ 1) * 16 + g + 8];
+    if (cq == 0) xm[part * 16 + g] = l[0], xm[part * 16 + g + 8] = l[1];
+    group_sync<NW>(rg);
+    l[0] = l[1] = 0.f;                                         // every warp forms the same sum, in the same order
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+        l[0] += xm[w * 16 + g];
+        l[1] += xm[w * 16 + g + 8];
+    }
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
         const int r = x ? row_b : row_a;
@@ -252,18 +285,18 @@ latent_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_r
         if (tq >= n_tq || n >= H) continue;
         const int t = tok0 + tq;
         if (splits == 1) {
-            bf16* dst = out + ((size_t)n * head_rows + t) * C + half * CW;
+            bf16* dst = out + ((size_t)n * head_rows + t) * C + part * CW;
             const float inv = 1.0f / l[x];
 #pragma unroll
             for (int i = 0; i < NO; ++i)
                 *reinterpret_cast<uint32_t*>(dst + i * 8 + cq * 2) = pack_bf16(o[i][2 * x] * inv, o[i][2 * x + 1] * inv);
         } else {
             const size_t item = ((size_t)t * H + n) * splits + split;
-            float* dst = part_o + item * C + half * CW;
+            float* dst = part_o + item * C + part * CW;
 #pragma unroll
             for (int i = 0; i < NO; ++i)
                 *reinterpret_cast<float2*>(dst + i * 8 + cq * 2) = make_float2(o[i][2 * x], o[i][2 * x + 1]);
-            if (half == 0 && cq == 0) part_ml[item * 2] = m[x], part_ml[item * 2 + 1] = l[x];
+            if (part == 0 && cq == 0) part_ml[item * 2] = m[x], part_ml[item * 2 + 1] = l[x];
         }
     }
 }
@@ -310,14 +343,14 @@ latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ 
     }
 }
 
-template <int C, int ROWG, int STAGES>
+template <int C, int ROWG, int STAGES, int NW>
 int launch_one(const float* q_lat, const float* q_rot, long long head_rows, bf16* out, float* part_o, float* part_ml,
                const bf16* cache, const int* block_table, int max_blocks, const int* entry_q_start, const int* entry_q_len,
                const int* entry_pos0, int entry_first, int n_entries, int n_tiles, int TQ, int HC, int H, int R,
                int page_size, float scale, int chunk, int splits, cudaStream_t stream) {
-    auto kern = latent_mma_kernel<C, ROWG, STAGES>;
+    auto kern = latent_mma_kernel<C, ROWG, STAGES, NW>;
     const int LD = C + R + 8;
-    const size_t sh = (size_t)(ROWG * 16 + STAGES * KT) * LD * sizeof(bf16) + (size_t)ROWG * (64 * 16 + 32 * 4);
+    const size_t sh = (size_t)(ROWG * 16 + STAGES * KT) * LD * sizeof(bf16) + (size_t)ROWG * (256 + 64) * 4;
     if (sh > 48 * 1024) {
         cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sh);
         if (err != cudaSuccess) {
@@ -326,7 +359,7 @@ int launch_one(const float* q_lat, const float* q_rot, long long head_rows, bf16
         }
     }
     const dim3 grid(n_tiles, (H + HC - 1) / HC, splits);
-    kern<<<grid, ROWG * 64, sh, stream>>>(q_lat, q_rot, head_rows, out, part_o, part_ml, cache, block_table, max_blocks,
+    kern<<<grid, ROWG * NW * 32, sh, stream>>>(q_lat, q_rot, head_rows, out, part_o, part_ml, cache, block_table, max_blocks,
                                           entry_q_start, entry_q_len, entry_pos0, entry_first, n_entries, TQ, HC, H, R,
                                           page_size, scale * 1.4426950408889634f, chunk, splits);
     return 0;
@@ -364,7 +397,7 @@ int infero_latent_attention_mma(const float* q_lat, const float* q_rot, long lon
     const int rowg = single ? HC / 16 : 4;
     int rc = 1;
 #define GO(C_, ROWG_, ST_)                                                                                              \
-    rc = launch_one<C_, ROWG_, ST_>(q_lat, q_rot, head_rows, (bf16*)out, part_o, part_ml, (const bf16*)cache, block_table, \
+    rc = launch_one<C_, ROWG_, ST_, (C_ >= 256 && ROWG_ < 4 ? 4 : 2)>(q_lat, q_rot, head_rows, (bf16*)out, part_o, part_ml, (const bf16*)cache, block_table, \
                                     max_blocks, entry_q_start, entry_q_len, entry_pos0, entry_first, n_entries, n_tiles, TQ, \
                                     HC, H, R, page_size, scale, chunk, splits, stream)
 #define BY_ROWS(C_)                                  \
