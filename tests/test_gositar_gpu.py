@@ -156,7 +156,7 @@ def test_rotary_tables_on_the_device_and_both_pairings():
             assert _rel(got[C:], PG.rotate(row[t:t + 1, C:].unsqueeze(1), torch.tensor([p]), freqs, amp, pairing)[0, 0]) < 2e-6
 
 
-@pytest.mark.parametrize("E,top,groups,keep", [(8, 3, 4, 2), (6, 3, 3, 2), (16, 4, 4, 3), (5, 5, 1, 1), (12, 1, 6, 1), (9, 2, 3, 3), (64, 8, 8, 4), (8, 2, 4, 2)])
+@pytest.mark.parametrize("E,top,groups,keep", [(8, 3, 4, 2), (6, 3, 3, 2), (16, 5, 4, 3), (5, 5, 1, 1), (12, 1, 6, 1), (9, 2, 3, 3), (64, 8, 8, 4), (8, 2, 4, 2)])
 def test_routing_with_groups_and_a_correction(E, top, groups, keep):
     """Choice and weights against the plain statement.  The corrections are large and mostly negative, so pick scores
     are negative: a group that is shut out must count as minus infinity, not as 0."""
