@@ -12,7 +12,7 @@
 //
 // prepare: per token one block for the latent row and one per group of heads.  c = row[:C] / sqrt(mean(row[:C]^2) + eps) * w (32-bit); the first `rot` of the R
 //   rotated coordinates of the key part and of every head's query turn by position * freq[i], cos and sin times
-//   `amp` (frequency table and amplitude come from the host, so any scaling of the frequencies is the host's);
+//   `amp` (a 64-bit frequency table and the amplitude come from the host, so any scaling of the frequencies is the host's);
 //   pairing 0: coordinate i with i + rot/2, pairing 1: 2i with 2i + 1.  The row [c | key part] goes to the token's
 //   page, the plain query parts to q_plain (the element type of the step) and the rotated ones to q_rot (float32).
 // attention (this file: the any-type kernel, one warp per (token, head); keys in ascending chunks of 32 aligned to
@@ -25,31 +25,35 @@ namespace {
 
 constexpr int PREP_THREADS = 128;
 
-__device__ __forceinline__ void turn(float a, float b, float ang, float amp, float& ra, float& rb) {
+// The angle is position times frequency in 64-bit, brought into [-pi, pi] there and only then rounded: a 32-bit product
+// is off by its own size times 2^-24, which at position 1,000 is already 6e-5 of a turn's worth of radians.
+__device__ __forceinline__ void turn(float a, float b, double ang, float amp, float& ra, float& rb) {
+    const double two_pi = 6.283185307179586476925286766559;
+    ang -= two_pi * rint(ang / two_pi);
     float s, c;
-    sincosf(ang, &s, &c);
+    sincosf((float)ang, &s, &c);
     s *= amp, c *= amp;
     ra = a * c - b * s;
     rb = b * c + a * s;
 }
 
 // element i of a rotated part of width R: what it becomes at position p
-__device__ __forceinline__ float rotated(const float* __restrict__ part, int i, int rot, int pairing, float pos,
-                                         const float* __restrict__ freq, float amp) {
+__device__ __forceinline__ float rotated(const float* __restrict__ part, int i, int rot, int pairing, int pos,
+                                         const double* __restrict__ freq, float amp) {
     if (i >= rot) return part[i];
     int ia, ib;
     if (pairing) ia = i & ~1, ib = ia + 1;
     else ia = i < rot / 2 ? i : i - rot / 2, ib = ia + rot / 2;
     const int pair = pairing ? i >> 1 : ia;
     float ra, rb;
-    turn(part[ia], part[ib], pos * freq[pair], amp, ra, rb);
+    turn(part[ia], part[ib], (double)pos * freq[pair], amp, ra, rb);
     return i == ia ? ra : rb;
 }
 
 template <typename T>
 __global__ void __launch_bounds__(PREP_THREADS)
 latent_prepare_kernel(const float* __restrict__ proj, int proj_stride, int q_off, int kv_off,
-                      const float* __restrict__ norm_w, float eps, const float* __restrict__ freq, int rot, int pairing,
+                      const float* __restrict__ norm_w, float eps, const double* __restrict__ freq, int rot, int pairing,
                       float amp, const int* __restrict__ positions, const int* __restrict__ tok_entry,
                       const int* __restrict__ block_table, int max_blocks, int page_size, T* __restrict__ cache,
                       int write_cache, T* __restrict__ q_plain, float* __restrict__ q_rot, long long head_rows,
@@ -57,7 +61,7 @@ latent_prepare_kernel(const float* __restrict__ proj, int proj_stride, int q_off
     __shared__ float red[32];
     const int t = blockIdx.x;
     const float* row = proj + (size_t)t * proj_stride;
-    const float pos = (float)positions[t];
+    const int pos = positions[t];
     if (blockIdx.y == 0) {
         // the latent row
         if (!write_cache) return;
@@ -174,7 +178,7 @@ extern "C" {
 // proj float32 [T, proj_stride]: the query's H * (D + R) columns from q_off, the C + R columns of the latent row from
 // kv_off.  cache [pages, 1, page, C + R]; q_plain [H, head_rows, D] of the cache's type; q_rot float32 [H, head_rows, R].
 int infero_latent_prepare(const float* proj, int proj_stride, int q_off, int kv_off, const float* norm_w, float eps,
-                          const float* freq, int rot, int pairing, float amp, const int* positions, const int* tok_entry,
+                          const double* freq, int rot, int pairing, float amp, const int* positions, const int* tok_entry,
                           const int* block_table, int max_blocks, int page_size, void* cache, int dtype, int write_cache,
                           void* q_plain, float* q_rot, long long head_rows, int n_tokens, int H, int D, int R, int C,
                           cudaStream_t stream) {

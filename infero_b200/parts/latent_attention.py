@@ -40,7 +40,7 @@ class LatentAttention(Mixer):
             if spec.position.rotary_dim > self.R:
                 raise ValueError(f"{spec.position.rotary_dim} rotated coordinates in a part of {self.R}")
             self.rope = part_class("position", spec.position.kind)(spec.position)
-            if not hasattr(self.rope, "inv_freq"):
+            if not hasattr(self.rope, "inv_freq64"):
                 raise ValueError(f"latent attention needs a rotary table; position kind '{spec.position.kind}' has none")
             self.pairing = getattr(self.rope, "pairing", "half")
             self.amp = float(getattr(self.rope, "amplitude", 1.0))
@@ -90,7 +90,7 @@ class LatentAttention(Mixer):
         rows = -(-T // A.TILE) * A.TILE if (h.dtype == torch.bfloat16 and D % 8 == 0 and C % 8 == 0) else T
         q_plain = torch.empty((H, rows, D), dtype=h.dtype, device=dev)
         q_rot = torch.empty((H, rows, R), dtype=torch.float32, device=dev)
-        freq = self.rope.inv_freq(dev) if self.rope is not None else None
+        freq = self.rope.inv_freq64(dev) if self.rope is not None else None
         A.prepare(proj, self.q_off, self.kv_off, self.latent_norm, self.spec.norm_eps, freq, self.pairing, self.amp,
                   ctx.positions, ctx.tok_entry, table, kv.k, kv.page_size, q_plain, q_rot, T, H, D, R, C,
                   write_cache=slot.write_cache)

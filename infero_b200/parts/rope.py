@@ -41,12 +41,20 @@ class RopeNeox(PositionEncoding):
         if getattr(spec, "yarn", None):
             inv, self.amplitude = yarn_stretch(inv, spec.theta, spec.rotary_dim, *spec.yarn)
         self._inv_host = torch.from_numpy(inv.astype(np.float32))
+        self._inv_host64 = torch.from_numpy(np.ascontiguousarray(inv, dtype=np.float64))
         self._inv_dev = {}
 
     def inv_freq(self, device) -> torch.Tensor:
         key = str(device)
         if key not in self._inv_dev:
             self._inv_dev[key] = self._inv_host.to(device)
+        return self._inv_dev[key]
+
+    def inv_freq64(self, device) -> torch.Tensor:
+        """The table as it was made, in 64-bit, for kernels that form the angle in 64-bit."""
+        key = ("f64", str(device))
+        if key not in self._inv_dev:
+            self._inv_dev[key] = self._inv_host64.to(device)
         return self._inv_dev[key]
 
 

@@ -364,7 +364,7 @@ def time_gositar_kernels(z, T, context, batch, timer, peaks):
         note(f"per_head_up_v_{label}", ms, 2.0 * H * C * V + H * rows_h * (2.0 * C + 4.0 * V), 2.0 * H * rows_h * C * V)
         # ---- prepare beside rotary + cache append --------------------------------------------------------------------
         width = H * (D + R) + C + R + H
-        proj, nw, fr = rnd(n, width, dtype=torch.float32), torch.ones(C, device=dev), torch.rand(R // 2, device=dev)
+        proj, nw, fr = rnd(n, width, dtype=torch.float32), torch.ones(C, device=dev), torch.rand(R // 2, device=dev, dtype=torch.float64)
         ms = timer(lambda: LA.prepare(proj, 0, H * (D + R), nw, 1e-5, fr, "adjacent", 1.2, ctx.positions, ctx.tok_entry, table, kv.k,
                                       16, q_plain, q_rot, n, H, D, R, C))
         note(f"latent_prepare_{label}", ms, n * (4.0 * width + 2.0 * (C + R) + H * (2.0 * D + 4.0 * R)))

@@ -142,15 +142,15 @@ def test_rotary_tables_on_the_device_and_both_pairings():
             table[t, p // page] = t
         q_plain, q_rot = torch.empty(H, T, D, device=DEV), torch.empty(H, T, R, device=DEV)
         w = 1 + 0.1 * torch.randn(C, generator=g)
-        A.prepare(proj.to(DEV), 0, H * (D + R), w.to(DEV), 1e-5, rope.inv_freq(DEV), pairing, rope.amplitude, _i32(pos),
+        A.prepare(proj.to(DEV), 0, H * (D + R), w.to(DEV), 1e-5, rope.inv_freq64(DEV), pairing, rope.amplitude, _i32(pos),
                   _i32(range(T)), table.to(DEV), cache, page, q_plain, q_rot, T, H, D, R, C)
         q = proj[:, :H * (D + R)].double().view(T, H, D + R)
         assert _rel(q_plain.permute(1, 0, 2), q[..., :D]) < 1e-6
-        # (sin and cos of 40000 * f in 32-bit: the angle itself is rounded to 2^-8 there)
-        assert _rel(q_rot.permute(1, 0, 2), PG.rotate(q[..., D:], torch.tensor(pos), freqs, amp, pairing)) < 3e-3
-        assert _rel(q_rot.permute(1, 0, 2)[:3], PG.rotate(q[..., D:], torch.tensor(pos), freqs, amp, pairing)[:3]) < 2e-6
+        # (the angle is formed in 64-bit and reduced before it is rounded: position 40,000 is as exact as position 1)
+        assert torch.allclose(rope.inv_freq64("cpu"), freqs, rtol=1e-14, atol=0)
+        assert _rel(q_rot.permute(1, 0, 2), PG.rotate(q[..., D:], torch.tensor(pos), freqs, amp, pairing)) < 2e-6
         row = proj[:, H * (D + R):].double()
-        for t, p in enumerate(pos[:3]):
+        for t, p in enumerate(pos):
             got = cache[t, 0, p % page].cpu()
             assert _rel(got[:C], PG.rms_norm(row[t, :C], w.double(), 1e-5)) < 2e-6
             assert _rel(got[C:], PG.rotate(row[t:t + 1, C:].unsqueeze(1), torch.tensor([p]), freqs, amp, pairing)[0, 0]) < 2e-6
